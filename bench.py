@@ -1,0 +1,347 @@
+#!/usr/bin/env python3
+"""Benchmark of the HXQ compressed-linear forward path on B200.
+
+Workload (BASELINE configs[1]): the grouped-affine HXQ linears of a
+Qwen2.5-7B MLP - gate/up [18944, 3584] and down [3584, 18944], k=256 codebook,
+group-128 fp32 scale/offset, ~0.1 % outlier sidecar - for every one of L layers
+with DISTINCT weights, M=1 bf16 activations.  One step = one pass over all 3*L
+linears (3*L kernel launches, ~73 MB of indices each, far larger than L2
+together).  Metric: algorithmic GB/s of the VQ-GEMV.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--layers L] [--m M]
+    python bench.py --impl reference      # the CPU path, timed on the host cores
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, INTER, GROUP = 3584, 18944, 128
+METRIC = "hxq_vq_gemv_algorithmic_GBps_M1_qwen2.5-7b_mlp"
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_layers(n_layers: int, device, seed0: int = 0, tp_rank: int = 0, tp_world: int = 1):
+    """Distinct compressed gate/up/down modules per layer (column-parallel
+    gate/up and row-parallel down when tp_world > 1)."""
+    import torch
+    from helix_substrate_b200 import HelixLinear
+    from helix_substrate_b200.hxq_writer_gpu import compress_weight, student_t_weight
+    from helix_substrate_b200.tp import shard_helix_linear
+    layers = []
+    for l in range(n_layers):
+        mods = {}
+        for j, (name, shape) in enumerate((("gate", (INTER, HIDDEN)), ("up", (INTER, HIDDEN)),
+                                           ("down", (HIDDEN, INTER)))):
+            w = student_t_weight(shape, seed0 + 3 * l + j, device)
+            enc = compress_weight(w, percentile=99.95, group_size=GROUP)
+            del w
+            mod = HelixLinear(shape[1], shape[0], tensor_name=f"model.layers.{l}.mlp.{name}_proj.weight", **enc)
+            if tp_world > 1:
+                mod = shard_helix_linear(mod, "row" if name == "down" else "column", tp_rank, tp_world)
+            mods[name] = mod.to(device)
+        layers.append(mods)
+        torch.cuda.empty_cache()
+    return layers
+
+
+def algorithmic_bytes(layers, M: int, act_bytes: int) -> int:
+    return sum(mod.packed().algorithmic_bytes(M, act_bytes, act_bytes)
+               for lay in layers for mod in lay.values())
+
+
+def cpu_forward_sample(seconds_target: float = 15.0, threads=None):
+    """The reference's CPU path (gather, group affine, fp32 matmul in 256-row
+    tiles: the oracle's restatement of HelixLinear._forward_naive with
+    affine_group_matmul_reference semantics) timed on the host cores for one
+    MLP layer's three linears at M=1."""
+    import numpy as np
+    import torch
+    from oracle import hxq_oracle as O
+    n_thr = threads or len(os.sched_getaffinity(0))
+    torch.set_num_threads(n_thr)
+    rng = np.random.default_rng(0)
+    cases = []
+    for shape in ((INTER, HIDDEN), (INTER, HIDDEN), (HIDDEN, INTER)):
+        n_out, n_in = shape
+        cb = np.sort(rng.standard_normal(256)).astype(np.float32) * 0.02
+        idx = rng.integers(0, 256, shape, dtype=np.uint8)
+        s = (1 + 0.1 * rng.standard_normal((n_out, n_in // GROUP))).astype(np.float32)
+        t = (0.002 * rng.standard_normal((n_out, n_in // GROUP))).astype(np.float32)
+        nnz = n_out * n_in // 1000
+        pos = np.sort(rng.choice(n_out * n_in, nnz, replace=False))
+        rows, cols = pos // n_in, pos % n_in
+        deltas = (0.05 * rng.standard_normal(nnz)).astype(np.float32)
+        x = rng.standard_normal((1, n_in)).astype(np.float32)
+        cases.append((x, cb, idx, rows, cols, deltas, s, t))
+    nbytes = sum(c[2].size + 1024 + c[6].size * 8 + len(c[3]) * 8 + (c[2].shape[0] + 1) * 4
+                 + 2 * c[2].shape[1] + 2 * c[2].shape[0] for c in cases)
+
+    def one_pass():
+        for (x, cb, idx, rows, cols, deltas, s, t) in cases:
+            O.forward_naive_torch(x, cb, idx, rows, cols, deltas, None, s, t, GROUP)
+
+    one_pass()
+    t0 = time.perf_counter()
+    one_pass()
+    dt1 = time.perf_counter() - t0
+    reps = max(2, min(50, int(seconds_target / max(dt1, 1e-3))))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    med = times[len(times) // 2]
+    return {"value": nbytes / med / 1e9, "unit": "GB/s", "cores": n_thr, "kind": "port",
+            "sample": f"1 of the MLP layers (gate+up+down, M=1, fp32), median of {reps} passes, "
+                      f"{med * 1e3:.1f} ms per pass", "ms_per_layer": med * 1e3, "bytes": nbytes}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    cpu = cpu_forward_sample(seconds_target=max(3.0, 1.5 * args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cpu["ms_per_layer"] * args.layers,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "qwen2.5-7b MLP gate/up/down HXQ linears (k=256, group-128 affine, 0.1% sidecar), "
+                               "M=1; CPU restatement of the reference's _forward_naive timed on one layer",
+                   "layers": args.layers, "m": 1},
+        "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--impl", default="hxq_b200")
+    ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    M, L, K, W = args.m, args.layers, args.steps, max(3, args.warmup)
+    layers = build_layers(L, dev, tp_rank=rank, tp_world=world)
+    act = torch.bfloat16
+    hid_local = layers[0]["down"].in_features       # INTER / world (row-parallel input slice)
+    x_h = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(1)).to(act).pin_memory()
+    xd_h = torch.randn(M, hid_local, generator=torch.Generator().manual_seed(2 + rank)).to(act).pin_memory()
+    x, xd = x_h.to(dev), xd_h.to(dev)
+    outs = [{k: torch.empty(M, m.out_features, device=dev, dtype=act) for k, m in lay.items()} for lay in layers]
+    n_launch_per_step = 3 * L * (-(-M // 4) if M > 4 else 1)
+
+    def step_kernels():
+        """One pass over every linear, straight on the packed weights (C ABI)."""
+        for lay, o in zip(layers, outs):
+            lay["gate"].packed().matmul(x, out=o["gate"])
+            lay["up"].packed().matmul(x, out=o["up"])
+            lay["down"].packed().matmul(xd, out=o["down"])
+            if world > 1:
+                dist.all_reduce(o["down"])
+
+    for _ in range(2):
+        step_kernels()
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step_kernels()
+            with torch.cuda.graph(graph, stream=side):
+                step_kernels()
+        torch.cuda.current_stream().wait_stream(side)
+    run = graph.replay if graph is not None else step_kernels
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        run()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for _ in range(K):
+            run()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if K * ms < 400:  # keep the sampler alive long enough to see clocks under load
+            t_end = time.perf_counter() + 0.5
+            while time.perf_counter() < t_end:
+                run()
+            torch.cuda.synchronize()
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / K
+
+    # ---- end to end through the module API with host buffers ----
+    def step_e2e():
+        xg = x_h.to(dev, non_blocking=True)
+        xdd = xd_h.to(dev, non_blocking=True)
+        y = None
+        for lay in layers:
+            g = lay["gate"](xg)
+            u = lay["up"](xg)
+            y = lay["down"](xdd)
+            if world > 1:
+                dist.all_reduce(y)
+        return g.to("cpu", non_blocking=True), u.to("cpu", non_blocking=True), y.to("cpu", non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step_e2e()
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    ms_e2e = float(te.item()) / K
+
+    nbytes_rank = algorithmic_bytes(layers, M, 2)
+    nb = torch.tensor([float(nbytes_rank)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(nb)
+    nbytes = float(nb.item())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = _peaks()
+    value = nbytes / (ms_step * 1e-3) / 1e9
+    per_gpu = value / world
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "qwen2.5-7b MLP gate/up [18944,3584] + down [3584,18944] HXQ linears "
+                               "(k=256 codebook, group-128 fp32 affine, two-sided 99.95% sidecar), distinct "
+                               f"weights per layer, M={M} bf16 activations",
+                   "layers": L, "m": M, "launch": "python" if graph is None else "cuda_graph",
+                   "parallelism": f"tp{world}" if world > 1 else "single",
+                   "l2": f"inputs larger than L2 ({nbytes_rank / 1e9:.2f} GB of distinct weights per pass)",
+                   "algorithmic_bytes_per_step": nbytes},
+        "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": (x_h.numel() + xd_h.numel()) * 2,
+                "d2h_bytes_per_step": M * (2 * layers[0]["gate"].out_features + HIDDEN) * 2,
+                "api": "HelixLinear.forward per linear, pinned host activations in, last layer's outputs out"},
+        "gpu_launches": n_launch_per_step * K,
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8TBps": per_gpu / 8000.0, "traffic": None,
+                     "kernel": "hxq::gemv_kernel<1>" if M == 1 else "hxq::gemv_kernel",
+                     "algorithmic_bytes_per_launch": nbytes_rank / (3 * L),
+                     "avg_launch_us": ms_step * 1e3 / (3 * L)},
+        "clocks": clk.summary(),
+    }
+    if not args.no_cpu_baseline and world == 1:
+        cpu = cpu_forward_sample(seconds_target=12.0)
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

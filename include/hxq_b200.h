@@ -1,0 +1,147 @@
+/*
+ * hxq_b200.h - C ABI of libhxq_b200.so: the HXQ compressed-linear forward path
+ * (uint8 indices into a 256-entry fp32 codebook, optional per-group affine
+ * scale/offset, sparse outlier sidecar) as hand-written sm_100a CUDA kernels.
+ *
+ * Weight definition shared by every entry point (o = output row, i = local
+ * input column of this shard):
+ *
+ *     W^[o, i] = cb[idx[o, i]] * s[o, g(i)] + t[o, g(i)],
+ *     g(i)     = (col0 + i) / group_size - col0 / group_size
+ *
+ * with s == 1, t == 0 when group_size == 0.  Matrix products add the sidecar
+ * as deltas (value - W^ at that position); hxq_dequant overwrites with values.
+ *
+ * Conventions: every pointer in hxq_desc and every x / y / out / workspace
+ * pointer is a DEVICE pointer borrowed for the duration of the call; nothing
+ * is allocated, freed or synchronised inside the library (except where an
+ * entry point says otherwise); kernels are enqueued on the caller's stream.
+ * All entry points return 0 on success or a negative HXQ_E_* code and never
+ * throw, trap or abort.
+ */
+#ifndef HXQ_B200_H_
+#define HXQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define HXQ_OK            0
+#define HXQ_E_ARG        -1  /* null pointer / bad enum / bad M                    */
+#define HXQ_E_SHAPE      -2  /* shape the kernels do not cover                     */
+#define HXQ_E_ALIGN      -3  /* pointer or leading dimension not aligned as stated  */
+#define HXQ_E_DTYPE      -4  /* unsupported element type                           */
+#define HXQ_E_DEVICE     -5  /* CUDA runtime error before launch (device, attrs)   */
+#define HXQ_E_LAUNCH     -6  /* kernel launch failed                               */
+#define HXQ_E_TIMEOUT    -7  /* a bounded device-side wait gave up                 */
+#define HXQ_E_WORKSPACE  -8  /* workspace missing or too small                     */
+
+/* element types of x, y, out, scales/offsets */
+#define HXQ_F32   0
+#define HXQ_F16   1
+#define HXQ_BF16  2
+
+typedef void* hxq_stream_t; /* a cudaStream_t */
+
+/*
+ * One compressed weight matrix (or a tensor-parallel shard of one).
+ * Replaces the buffer set of the reference module HelixLinear
+ * (helix_substrate/helix_linear.py:166-239: codebook, indices,
+ * _sidecar_rows/_cols/_deltas, bias) and the scales/offsets arguments of
+ * fused_affine_group_matmul (helix_substrate/triton_affine_group_matmul.py:301-308).
+ */
+typedef struct hxq_desc {
+    int32_t out_features;  /* rows of this shard                                          */
+    int32_t in_features;   /* columns of this shard                                       */
+    int32_t col0;          /* global column of local column 0 (row-parallel shards), else 0 */
+    int32_t group_size;    /* affine group length along the input dim, 0 = no affine      */
+    int64_t ld_idx;        /* row stride of indices in bytes (>= in_features)             */
+    const uint8_t* indices;/* [out_features, ld_idx] uint8                                */
+    const float* codebook; /* [256] fp32                                                  */
+    const void* scales;    /* [out_features, ld_st] of st_dtype, NULL when group_size==0  */
+    const void* offsets;   /* same layout as scales                                       */
+    int32_t st_dtype;      /* HXQ_F32 or HXQ_F16                                          */
+    int32_t ld_st;         /* row stride of scales/offsets in elements                    */
+    const int32_t* rowptr; /* [out_features+1] CSR row pointer of the sidecar, NULL = none */
+    const int32_t* cols;   /* [nnz] local column of each sidecar entry, row-sorted        */
+    const float* deltas;   /* [nnz] value - W^ at the position (used by gemv / gemm)      */
+    const float* values;   /* [nnz] exact value at the position (used by dequant)         */
+    const float* bias;     /* [out_features] fp32 or NULL                                 */
+} hxq_desc;
+
+/* Library version as major*10000 + minor*100 + patch. */
+int hxq_version(void);
+
+/* Static, human-readable text for a status code. */
+const char* hxq_strerror(int status);
+
+/*
+ * Dequantise rows [row0, row1) to out[(row - row0) * ld_out + i].
+ * out_dtype HXQ_F32 is bit-exact with CDNAv3Reader.reconstruct() /
+ * reconstruct_block() (helix_substrate/hxq_reader_v3.py:102-187): codebook
+ * gather, then the sidecar VALUE overwrites the entry.  HXQ_BF16 / HXQ_F16
+ * round that fp32 result once.  Also serves HelixLinear.decode_weight /
+ * _dequant_tile (helix_substrate/helix_linear.py:735-781,881-888) and the
+ * "buffered" materialisation (helix_linear.py:556-634).
+ */
+int hxq_dequant(const hxq_desc* d, int32_t row0, int32_t row1,
+                void* out, int out_dtype, int64_t ld_out, hxq_stream_t stream);
+
+/*
+ * Bytes of zero-initialised device workspace hxq_gemv needs for this shape
+ * (split-K partial sums and arrival counters).  The workspace must be zero
+ * before its first use; hxq_gemv leaves the counters zero again on return, so
+ * one workspace can be reused by successive calls on the same stream.  Calls
+ * that may overlap on the GPU need separate workspaces.
+ */
+size_t hxq_gemv_workspace_bytes(const hxq_desc* d, int32_t M);
+
+/*
+ * Decode-time product for M <= 16 tokens:  y[m, o] = sum_i x[m, i] * W^[o, i]
+ * + sidecar + bias, fp32 accumulation, result rounded once to y_dtype.
+ * Replaces fused_vq_matmul at N <= 16 (helix_substrate/triton_vq_matmul.py:521-727:
+ * _vq_decode_dotprod_kernel + _sidecar_fused_kernel + bias) and
+ * fused_affine_group_matmul's decode kernel
+ * (helix_substrate/triton_affine_group_matmul.py:112-177,301-363).
+ * x is [M, ldx] of x_dtype, y is [M, ldy] of y_dtype (strides in elements).
+ */
+int hxq_gemv(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx,
+             void* y, int y_dtype, int64_t ldy,
+             void* workspace, size_t workspace_bytes, hxq_stream_t stream);
+
+/*
+ * Prefill-time product for any M (meant for M >= 17):  same contract as
+ * hxq_gemv but weights are dequantised to bf16 tiles in shared memory and
+ * contracted on the tcgen05 tensor cores with fp32 TMEM accumulators.
+ * Replaces fused_vq_matmul at N > 16 (_vq_gather_matmul_tiled_kernel,
+ * helix_substrate/triton_vq_matmul.py:249-334,634-661, + scatter_add sidecar
+ * :693-698) and _affine_group_tiled_kernel
+ * (helix_substrate/triton_affine_group_matmul.py:32-109).
+ * status_word: device int32 the kernel sets non-zero if a bounded wait gave
+ * up (the host reads it after synchronising); may be NULL.
+ */
+size_t hxq_gemm_workspace_bytes(const hxq_desc* d, int32_t M);
+int hxq_gemm(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx,
+             void* y, int y_dtype, int64_t ldy,
+             void* workspace, size_t workspace_bytes, int32_t* status_word,
+             hxq_stream_t stream);
+
+/*
+ * Host helper: CSR row pointer from ascending flat positions
+ * (rows = pos / in_features), the derivation HelixLinear does at load
+ * (helix_substrate/helix_linear.py:196-203,960-997).  positions, rowptr and
+ * cols are HOST pointers; rowptr has out_features+1 entries, cols nnz entries.
+ * Fails with HXQ_E_ARG if positions are not strictly ascending or out of range.
+ */
+int hxq_csr_from_positions(const int64_t* positions, int64_t nnz,
+                           int32_t out_features, int32_t in_features,
+                           int32_t* rowptr, int32_t* cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HXQ_B200_H_ */

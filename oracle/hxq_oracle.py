@@ -334,3 +334,43 @@ def shard_cols(n_in, rank, world):
     """Row-parallel: contiguous slice of input columns."""
     per = (n_in + world - 1) // world
     return min(rank * per, n_in), min((rank + 1) * per, n_in)
+
+
+# ---------------------------------------------------------------------------
+# Timed CPU baseline: the same operator with the reference's own torch ops
+# ---------------------------------------------------------------------------
+
+def forward_naive_torch(x, codebook, indices, rows=None, cols=None, deltas=None, bias=None,
+                        scales=None, offsets=None, group_size=0, chunk=256):
+    """HelixLinear._forward_naive with the torch calls the reference makes
+    (helix_linear.py:735-822: ``codebook[idx.long()]`` gather per 256-row tile,
+    in-place sidecar add, ``x @ W_tile.t()`` in fp32), plus the group affine of
+    affine_group_matmul_reference (triton_affine_group_matmul.py:375-379) for the
+    grouped configurations.  Used only as the timed CPU baseline: it runs on all
+    the threads torch is given."""
+    import torch
+    cb = torch.as_tensor(codebook)
+    idx = torch.as_tensor(indices)
+    n_out, n_in = idx.shape
+    x2 = torch.as_tensor(x).reshape(-1, n_in).float()
+    out = torch.zeros(x2.shape[0], n_out, dtype=torch.float32)
+    if rows is not None:
+        rows_t, cols_t, deltas_t = (torch.as_tensor(a) for a in (rows, cols, deltas))
+    if scales is not None:
+        s_t, t_t = torch.as_tensor(scales).float(), torch.as_tensor(offsets).float()
+    for r0 in range(0, n_out, chunk):
+        r1 = min(r0 + chunk, n_out)
+        tile = cb[idx[r0:r1].long()]
+        if scales is not None:
+            ng = n_in // group_size
+            tile = (tile.reshape(r1 - r0, ng, group_size) * s_t[r0:r1, :, None]
+                    + t_t[r0:r1, :, None]).reshape(r1 - r0, n_in)
+        if rows is not None:
+            mask = (rows_t >= r0) & (rows_t < r1)
+            if mask.any():
+                tile = tile.clone()
+                tile[rows_t[mask] - r0, cols_t[mask]] += deltas_t[mask]
+        out[:, r0:r1] = x2 @ tile.t()
+    if bias is not None:
+        out += torch.as_tensor(bias).unsqueeze(0)
+    return out.numpy()

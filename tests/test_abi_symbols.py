@@ -1,0 +1,59 @@
+"""The C-ABI library loads on a machine without a GPU and exports every entry
+point include/hxq_b200.h declares; argument validation works without a device."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared():
+    text = (ROOT / "include" / "hxq_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hxq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from helix_substrate_b200 import _lib
+    L = _lib.lib()
+    names = _declared()
+    assert {"hxq_version", "hxq_strerror", "hxq_dequant", "hxq_gemv", "hxq_gemm",
+            "hxq_gemv_workspace_bytes", "hxq_gemm_workspace_bytes", "hxq_csr_from_positions"} <= set(names)
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in the header but not exported"
+    assert L.hxq_version() >= 100
+    assert _lib.strerror(0) == "ok" and "workspace" in _lib.strerror(_lib.HXQ_E_WORKSPACE)
+
+
+def test_descriptor_layout_matches_header():
+    from helix_substrate_b200._lib import HxqDesc
+    # 4 x int32, int64, 4 pointers, 2 x int32, 5 pointers
+    assert C.sizeof(HxqDesc) == 16 + 8 + 32 + 8 + 40
+    assert HxqDesc.ld_idx.offset == 16 and HxqDesc.st_dtype.offset == 56 and HxqDesc.rowptr.offset == 64
+
+
+def test_argument_validation_without_a_device():
+    from helix_substrate_b200 import _lib
+    L = _lib.lib()
+    d = _lib.HxqDesc()
+    assert L.hxq_gemv(C.byref(d), None, 0, 1, 0, None, 0, 0, None, 0, None) == _lib.HXQ_E_ARG
+    assert L.hxq_dequant(None, 0, 1, None, 0, 0, None) == _lib.HXQ_E_ARG
+    assert L.hxq_gemv_workspace_bytes(C.byref(d), 1) == 0
+
+
+def test_csr_helper():
+    from helix_substrate_b200 import _lib
+    L = _lib.lib()
+    pos = np.array([3, 40, 41, 2047], dtype=np.int64)
+    rp = np.empty(65, dtype=np.int32)
+    cols = np.empty(4, dtype=np.int32)
+    assert L.hxq_csr_from_positions(pos.ctypes.data, 4, 64, 32, rp.ctypes.data, cols.ctypes.data) == 0
+    assert rp[0] == 0 and rp[1] == 1 and rp[2] == 3 and rp[63] == 3 and rp[64] == 4
+    assert cols.tolist() == [3, 8, 9, 31]
+    bad = np.array([5, 5], dtype=np.int64)
+    assert L.hxq_csr_from_positions(bad.ctypes.data, 2, 64, 32, rp.ctypes.data, cols.ctypes.data) == _lib.HXQ_E_ARG
+    assert L.hxq_csr_from_positions(None, 0, 64, 32, rp.ctypes.data, None) == 0 and rp[64] == 0
