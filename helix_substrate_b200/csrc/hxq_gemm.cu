@@ -1,22 +1,421 @@
-// hxq_gemm: prefill-time product (placeholder body; see the tensor-core kernel below once built).
+// hxq_gemm: prefill-time product on the tcgen05 tensor cores.
+//
+//   D[o, m] = sum_k W^[o, k] * x[m, k]      (o: 128 output rows per CTA, m: BN tokens)
+//
+// Only here is the path a dense contraction, so only here tensor cores are used.
+// One CTA owns a 128 x BN output tile; per 64-column K step
+//
+//   warp 0   (1 lane)  TMA: 128x64 index bytes and BN x 64 bf16 activations (128-byte
+//                      swizzle) -> shared memory, completion on an mbarrier
+//   warps 2-9          dequantise the index tile to bf16 in the UMMA K-major
+//                      128B-swizzled layout: lane-replicated codebook lookup, group
+//                      affine in fp32, sidecar deltas folded in (each row's CSR cursor
+//                      walks forward as K advances), proxy fence, arrive
+//   warp 1   (1 lane)  4 x tcgen05.mma (K = 16 each) accumulating fp32 in TMEM;
+//                      tcgen05.commit frees the stage
+//
+// and after the last step warps 2-5 read TMEM (tcgen05.ld), add the bias and store
+// y[m, o].  Three stages; every mbarrier wait is bounded and raises a status word.
+// No cluster launch and no multicast anywhere.
+
+#include <cuda.h>
+
 #include "hxq_common.cuh"
+#include "hxq_sm100.cuh"
 
 namespace hxq {
+
 int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, void* y, int y_dtype,
                int64_t ldy, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemv_workspace_bytes(const hxq_desc* d, int32_t M);
+
+namespace gemm {
+
+constexpr int BM = 128;        // output rows per CTA = UMMA M
+constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzled row
+constexpr int STAGES = 3;
+constexpr int LUT_BYTES = 256 * 128;   // entry c, lane l at byte c*128 + l*4
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int IDX_BYTES = BM * BK;     // 8 KB
+constexpr int NUM_DEQ_WARPS = 8;
+constexpr int NUM_THREADS = 32 * (2 + NUM_DEQ_WARPS);
+
+template <int BN> struct Smem {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + IDX_BYTES;
+    static constexpr int BAR_OFFSET = LUT_BYTES + STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+};
+
+struct GemmArgs {
+    const float* cb;
+    const void* scales;
+    const void* offsets;
+    const int32_t* rowptr;
+    const int32_t* cols;
+    const float* deltas;
+    const float* bias;
+    void* y;
+    int32_t* status;
+    int64_t ldy;
+    int32_t out_features, in_features, col0, group_size, ld_st, st_dtype, n_groups;
+    int32_t M, y_dtype, k_steps;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
 }
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x,
+            const GemmArgs a) {
+    using S = Smem<BN>;
+    extern __shared__ char smem_raw[];
+    char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    char* lut = smem;
+    char* stage0 = smem + LUT_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+    uint64_t* tma_full = bars;                  // [STAGES] index + activation bytes landed
+    uint64_t* a_full = bars + STAGES;           // [STAGES] bf16 weight tile written
+    uint64_t* empty = bars + 2 * STAGES;        // [STAGES] UMMAs of the stage retired
+    uint64_t* acc_full = bars + 3 * STAGES;     // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BN;     // token tile (fastest: neighbours share the weight tile in L2)
+    const int o0 = blockIdx.y * BM;     // output-row tile
+    const int KS = a.k_steps;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            sm100::mbar_init(&tma_full[s], 1);
+            sm100::mbar_init(&a_full[s], NUM_DEQ_WARPS);
+            sm100::mbar_init(&empty[s], 1);
+        }
+        sm100::mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        sm100::fence_barrier_init();
+        sm100::prefetch_tensormap(&map_idx);
+        sm100::prefetch_tensormap(&map_x);
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc(tmem_slot, BN);
+        sm100::tmem_relinquish();
+    }
+    // codebook table for the dequantising warps: entry c, lane l at c*128 + l*4
+    for (int i = threadIdx.x; i < 256 * 32; i += NUM_THREADS)
+        *reinterpret_cast<float*>(lut + (i >> 5) * 128 + (i & 31) * 4) = a.cb[i >> 5];
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int armed = 0;
+            for (int ks = 0; ks < KS; ++ks) {
+                const int s = ks % STAGES;
+                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+                if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+                char* st = stage0 + s * S::STAGE_BYTES;
+                sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)(IDX_BYTES + S::B_BYTES));
+                sm100::tma_load_2d(st + A_BYTES + S::B_BYTES, &map_idx, &tma_full[s], ks * BK, o0);
+                sm100::tma_load_2d(st + A_BYTES, &map_x, &tma_full[s], ks * BK, m0);
+                armed = ks + 1;
+            }
+            if (*abort_flag != 0) {
+                // gave up: let copies already in flight land before the CTA retires
+                for (int ks = (armed > STAGES ? armed - STAGES : 0); ks < armed; ++ks)
+                    sm100::mbar_wait(&tma_full[ks % STAGES], (uint32_t)(ks / STAGES) & 1u, abort_flag, 200000000LL);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = sm100::make_idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int ks = 0; ks < KS && ok; ++ks) {
+                const int s = ks % STAGES;
+                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+                ok = sm100::mbar_wait(&tma_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
+                if (!ok) break;
+                sm100::tc_fence_after_sync();
+                char* st = stage0 + s * S::STAGE_BYTES;
+                const uint64_t da = sm100::make_desc_k_sw128(sm100::smem_u32(st));
+                const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(st + A_BYTES));
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)   // +32 bytes (>> 4 = 2) per 16-element K slice
+                    sm100::umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                sm100::umma_commit(&empty[s]);
+            }
+            if (ok) sm100::umma_commit(acc_full);
+        }
+    } else {
+        // ------------------------------------------------------------ dequantising warps
+        const int dw = warp - 2;                     // 0..7: rows [16*dw, 16*dw + 16)
+        const int r_a = 16 * dw + (lane >> 2);       // first pass row (local), second pass is r_a + 8
+        const int jc = lane & 3;                     // 16-column chunk of the 64-column step
+        const uint32_t lane4x2 = (uint32_t)lane << 3;
+        const bool affine = a.group_size > 0;
+        const int row_a = o0 + r_a, row_b = o0 + r_a + 8;
+        const bool ok_a = row_a < a.out_features, ok_b = row_b < a.out_features;
+
+        auto load_st = [&](int ks, int row, bool okr, float& s, float& t) {
+            s = 1.f; t = 0.f;
+            if (affine && okr) {
+                int g = (a.col0 + ks * BK) / a.group_size - a.col0 / a.group_size;
+                g = g < a.n_groups ? g : a.n_groups - 1;
+                const int64_t o = (int64_t)row * a.ld_st + g;
+                if (a.st_dtype == HXQ_F32) {
+                    s = reinterpret_cast<const float*>(a.scales)[o];
+                    t = reinterpret_cast<const float*>(a.offsets)[o];
+                } else {
+                    s = __half2float(reinterpret_cast<const __half*>(a.scales)[o]);
+                    t = __half2float(reinterpret_cast<const __half*>(a.offsets)[o]);
+                }
+            }
+        };
+        float sa, ta, sb, tb, sa_n, ta_n, sb_n, tb_n;
+        load_st(0, row_a, ok_a, sa_n, ta_n);
+        load_st(0, row_b, ok_b, sb_n, tb_n);
+
+        // sidecar cursor: lanes 0..15 each follow one of this warp's 16 rows
+        const int row_c = o0 + 16 * dw + lane;
+        int e_cur = 0, e_end = 0, nc = 0x7fffffff;
+        float nd = 0.f;
+        if (a.rowptr != nullptr && lane < 16 && row_c < a.out_features) {
+            e_cur = a.rowptr[row_c];
+            e_end = a.rowptr[row_c + 1];
+            if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
+        }
+
+        for (int ks = 0; ks < KS; ++ks) {
+            const int s = ks % STAGES;
+            const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+            sa = sa_n; ta = ta_n; sb = sb_n; tb = tb_n;
+            if (ks + 1 < KS) {  // next step's scale/offset go out before we block
+                load_st(ks + 1, row_a, ok_a, sa_n, ta_n);
+                load_st(ks + 1, row_b, ok_b, sb_n, tb_n);
+            }
+            if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
+            char* st = stage0 + s * S::STAGE_BYTES;
+            const char* idx_s = st + A_BYTES + S::B_BYTES;
+
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                const int r = r_a + 8 * pass;
+                const float sc = pass ? sb : sa, of = pass ? tb : ta;
+                const uint4 q = *reinterpret_cast<const uint4*>(idx_s + r * BK + jc * 16);
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    // ((code << 8) | lane*8) >> 1 = code*128 + lane*4
+                    const uint32_t off = __byte_perm(w[j >> 2], lane4x2, 0x5504u | (uint32_t)((j & 3) << 4)) >> 1;
+                    v[j] = fmaf(*reinterpret_cast<const float*>(lut + off), sc, of);
+                }
+                uint4 lo, hi;
+                lo.x = pack_bf16x2(v[0], v[1]);   lo.y = pack_bf16x2(v[2], v[3]);
+                lo.z = pack_bf16x2(v[4], v[5]);   lo.w = pack_bf16x2(v[6], v[7]);
+                hi.x = pack_bf16x2(v[8], v[9]);   hi.y = pack_bf16x2(v[10], v[11]);
+                hi.z = pack_bf16x2(v[12], v[13]); hi.w = pack_bf16x2(v[14], v[15]);
+                char* arow = st + r * 128;
+                *reinterpret_cast<uint4*>(arow + (((2 * jc) ^ (r & 7)) << 4)) = lo;
+                *reinterpret_cast<uint4*>(arow + (((2 * jc + 1) ^ (r & 7)) << 4)) = hi;
+            }
+            __syncwarp();
+
+            // sidecar entries of this warp's rows that fall into this K step
+            {
+                const int rr = lane & 15;                       // row (within the warp's 16) this lane follows
+                const int src = 4 * (rr & 7);                   // lane that holds that row's scale/offset
+                const float s0 = __shfl_sync(0xffffffffu, sa, src), t0 = __shfl_sync(0xffffffffu, ta, src);
+                const float s1 = __shfl_sync(0xffffffffu, sb, src), t1 = __shfl_sync(0xffffffffu, tb, src);
+                const float sc = (rr & 8) ? s1 : s0, of = (rr & 8) ? t1 : t0;
+                const int k_hi = (ks + 1) * BK;
+                while (nc < k_hi) {                              // nc >= ks*BK: the cursor only moves forward
+                    const int r = 16 * dw + rr;
+                    const int c = nc - ks * BK;
+                    const uint32_t code = (uint8_t)idx_s[r * BK + c];
+                    const float wv = fmaf(*reinterpret_cast<const float*>(lut + code * 128 + lane * 4), sc, of) + nd;
+                    *reinterpret_cast<__nv_bfloat16*>(st + r * 128 + ((((c >> 3) ^ (r & 7)) << 4) | ((c & 7) << 1))) =
+                        __float2bfloat16_rn(wv);
+                    ++e_cur;
+                    if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; } else { nc = 0x7fffffff; }
+                }
+            }
+            sm100::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) sm100::mbar_arrive(&a_full[s]);
+        }
+
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        if (warp < 6) {
+            const int quarter = warp & 3;            // TMEM lanes this warp may read: [32*quarter, +32)
+            const int row = o0 + 32 * quarter + lane;
+            const bool row_ok = row < a.out_features;
+            const float bias = (a.bias != nullptr && row_ok) ? a.bias[row] : 0.f;
+            if (sm100::mbar_wait(acc_full, 0u, abort_flag)) {
+                sm100::tc_fence_after_sync();
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (m0 + c0 >= a.M) break;       // warp-uniform
+                    uint32_t r[32];
+                    sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0, r);
+                    sm100::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int m = m0 + c0 + j;
+                        if (row_ok && m < a.M)
+                            store_from_f32(a.y, (int64_t)m * a.ldy + row, __uint_as_float(r[j]) + bias, a.y_dtype);
+                    }
+                }
+            }
+        }
+    }
+
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        sm100::tc_fence_after_sync();
+        sm100::tmem_dealloc(tmem_base, BN);
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0 && a.status != nullptr) atomicExch(a.status, HXQ_E_TIMEOUT);
+}
+
+}  // namespace gemm
+}  // namespace hxq
+
+// ---- host side ---------------------------------------------------------------------
+namespace hxq {
+namespace gemm {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// fp32 / fp16 activations -> contiguous bf16 [M, ld_out] (tensor-core operand type)
+__global__ void __launch_bounds__(256) to_bf16_kernel(const void* x, int x_dtype, int64_t ldx, int M, int K,
+                                                       __nv_bfloat16* out, int64_t ld_out) {
+    const int64_t total = (int64_t)M * ld_out;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / ld_out), k = (int)(i - (int64_t)m * ld_out);
+        out[i] = __float2bfloat16_rn(k < K ? load_as_f32(x, (int64_t)m * ldx + k, x_dtype) : 0.f);
+    }
+}
+
+bool fast_ok(const hxq_desc* d) {
+    return (d->in_features % 16 == 0) && (d->ld_idx % 16 == 0) && aligned_to(d->indices, 16) &&
+           (d->col0 % 64 == 0) && (d->group_size == 0 || d->group_size % 64 == 0) && encode_fn() != nullptr;
+}
+
+static int64_t x_pad(const hxq_desc* d) { return ((int64_t)d->in_features + 7) / 8 * 8; }
+
+size_t workspace_bytes(const hxq_desc* d, int32_t M) {
+    if (!fast_ok(d)) return gemv_workspace_bytes(d, 4);
+    return (size_t)M * x_pad(d) * 2 + 256;   // room for a bf16 copy of x when it is not usable in place
+}
+
+template <int BN>
+static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const GemmArgs& a, int grid_m, int grid_o,
+                  cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN>::TOTAL) !=
+            cudaSuccess)
+            return HXQ_E_DEVICE;
+        attr_set[dev] = true;
+    }
+    gemm_kernel<BN><<<dim3(grid_m, grid_o), NUM_THREADS, Smem<BN>::TOTAL, stream>>>(mi, mx, a);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, void* y, int y_dtype, int64_t ldy,
+        void* workspace, size_t ws_bytes, int32_t* status_word, cudaStream_t stream) {
+    const void* xb = x;
+    int64_t ldxb = ldx;
+    const bool x_in_place = (x_dtype == HXQ_BF16) && aligned_to(x, 16) && ((ldx * 2) % 16 == 0);
+    if (!x_in_place) {
+        const int64_t ld = x_pad(d);
+        if (!workspace || ws_bytes < (size_t)M * ld * 2) return HXQ_E_WORKSPACE;
+        if (!aligned_to(workspace, 16)) return HXQ_E_ALIGN;
+        int64_t total = (int64_t)M * ld;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        to_bf16_kernel<<<blocks, 256, 0, stream>>>(x, x_dtype, ldx, M, d->in_features,
+                                                   reinterpret_cast<__nv_bfloat16*>(workspace), ld);
+        if (cudaGetLastError() != cudaSuccess) return HXQ_E_LAUNCH;
+        xb = workspace;
+        ldxb = ld;
+    }
+    const int BN = M > 128 ? 256 : (M > 64 ? 128 : 64);
+    CUtensorMap mi, mx;
+    if (!make_map_2d(&mi, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->indices, (uint64_t)d->in_features,
+                     (uint64_t)d->out_features, (uint64_t)d->ld_idx, BK, BM, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return HXQ_E_DEVICE;
+    if (!make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, (uint64_t)d->in_features, (uint64_t)M,
+                     (uint64_t)ldxb * 2, BK, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return HXQ_E_DEVICE;
+    GemmArgs a;
+    a.cb = d->codebook; a.scales = d->scales; a.offsets = d->offsets;
+    a.rowptr = d->rowptr; a.cols = d->cols; a.deltas = d->deltas; a.bias = d->bias;
+    a.y = y; a.status = status_word; a.ldy = ldy;
+    a.out_features = d->out_features; a.in_features = d->in_features; a.col0 = d->col0;
+    a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
+    a.n_groups = d->group_size > 0
+                     ? (d->col0 + d->in_features - 1) / d->group_size - d->col0 / d->group_size + 1 : 0;
+    a.M = M; a.y_dtype = y_dtype;
+    a.k_steps = (d->in_features + BK - 1) / BK;
+    const int grid_o = (d->out_features + BM - 1) / BM;
+    const int grid_m = (M + BN - 1) / BN;
+    if (BN == 256) return launch<256>(mi, mx, a, grid_m, grid_o, stream);
+    if (BN == 128) return launch<128>(mi, mx, a, grid_m, grid_o, stream);
+    return launch<64>(mi, mx, a, grid_m, grid_o, stream);
+}
+
+}  // namespace gemm
+}  // namespace hxq
 
 extern "C" size_t hxq_gemm_workspace_bytes(const hxq_desc* d, int32_t M) {
     if (hxq::validate_desc(d) != HXQ_OK || M <= 0) return 0;
-    return hxq::gemv_workspace_bytes(d, 4);
+    return hxq::gemm::workspace_bytes(d, M);
 }
 
 extern "C" int hxq_gemm(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, void* y,
                         int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes,
-                        int32_t* status_word, hxq_stream_t stream) {
+                        int32_t* status_word, hxq_stream_t stream_) {
     using namespace hxq;
-    (void)status_word;
     int st = validate_desc(d);
     if (st != HXQ_OK) return st;
     if (!x || !y) return HXQ_E_ARG;
@@ -24,6 +423,8 @@ extern "C" int hxq_gemm(const hxq_desc* d, const void* x, int x_dtype, int32_t M
     if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return HXQ_E_DTYPE;
     if (ldx < d->in_features || ldy < d->out_features) return HXQ_E_SHAPE;
     if (d->rowptr && !d->deltas) return HXQ_E_ARG;
-    return gemv_any_m(d, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
-                      reinterpret_cast<cudaStream_t>(stream));
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!gemm::fast_ok(d))  // ragged or unaligned shapes: token groups through the decode kernels
+        return gemv_any_m(d, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
+    return gemm::run(d, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, status_word, stream);
 }

@@ -244,3 +244,91 @@ def test_full_size_properties(shape):
     lhs = mod(2.0 * x1 - 3.0 * x2)
     rhs = 2.0 * mod(x1) - 3.0 * mod(x2)
     assert rel_l2(lhs.cpu().numpy(), rhs.cpu().numpy()) < 1e-4
+
+
+# --------------------------------------------------------------------------- tensor-core path
+
+GEMM_SHAPES = [  # (OUT, IN, G, col0)
+    (128, 512, 128, 0), (200, 1024, 128, 0), (64, 3584, 128, 0), (300, 448, 128, 448),
+    (136, 1088, 64, 0), (128, 2048, 0, 0), (96, 592, 0, 0),
+]
+
+
+@pytest.mark.parametrize("shape", GEMM_SHAPES)
+@pytest.mark.parametrize("M", [17, 64, 100, 256, 300])
+def test_gemm_vs_oracle(shape, M):
+    n_out, n_in, G, col0 = shape
+    rng = np.random.default_rng(n_out * 31 + n_in + M)
+    cb, idx, pos, vals, b, s, t = _make(rng, n_out, n_in, 0, nnz_frac=0.004)
+    c0 = 0
+    if G:
+        ng = (col0 + n_in - 1) // G - col0 // G + 1
+        s = (1.0 + 0.1 * rng.standard_normal((n_out, ng))).astype(np.float32)
+        t = (0.002 * rng.standard_normal((n_out, ng))).astype(np.float32)
+        c0 = col0 - (col0 // G) * G
+    rows, cols, deltas = O.derive_sidecar(cb, idx, pos, vals, s, t, G, c0)
+    x = _t(rng.standard_normal((M, n_in)).astype(np.float32), torch.bfloat16)
+    ref = O.forward_f64(x.float().cpu().numpy(), cb, idx, rows, cols, deltas, b, s, t, G, c0)
+    w = _weight(cb, idx, pos, vals, b, s, t, G, col0)
+    y = w.matmul(x, out_dtype=torch.float32, force="gemm")
+    assert w.gemm_status() == 0, "a bounded wait inside the tensor-core kernel gave up"
+    assert rel_l2(y.cpu().numpy(), ref) < TOL_BF16
+    # the decode kernels agree with it to bf16 precision as well
+    y2 = w.matmul(x, out_dtype=torch.float32, force="gemv")
+    assert rel_l2(y.cpu().numpy(), y2.cpu().numpy()) < TOL_BF16
+    assert torch.equal(y, w.matmul(x, out_dtype=torch.float32, force="gemm"))
+
+
+def test_gemm_sidecar_is_applied():
+    """With a zero codebook the product is the sidecar alone: every entry must
+    land in the right (row, column) of the dequantised tile."""
+    rng = np.random.default_rng(2)
+    n_out, n_in, M = 256, 1024, 64
+    cb = np.zeros(256, np.float32)
+    idx = rng.integers(0, 256, (n_out, n_in), dtype=np.uint8)
+    nnz = 2000
+    pos = np.sort(rng.choice(n_out * n_in, nnz, replace=False)).astype(np.int64)
+    vals = rng.standard_normal(nnz).astype(np.float16).astype(np.float32)
+    dense = np.zeros(n_out * n_in, np.float32)
+    dense[pos] = vals
+    x = _t(rng.standard_normal((M, n_in)).astype(np.float32), torch.bfloat16)
+    ref = x.float().cpu().numpy().astype(np.float64) @ dense.reshape(n_out, n_in).astype(np.float64).T
+    w = _weight(cb, idx, pos, vals)
+    y = w.matmul(x, force="gemm")
+    assert w.gemm_status() == 0
+    assert rel_l2(y.cpu().numpy(), ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("xdt", [torch.float32, torch.float16])
+def test_gemm_converts_other_activation_types(xdt):
+    rng = np.random.default_rng(9)
+    cb, idx, pos, vals, b, s, t = _make(rng, 128, 1000 // 8 * 8 + 16, 0)
+    rows, cols, deltas = O.derive_sidecar(cb, idx, pos, vals)
+    x = torch.randn(40, idx.shape[1], device=DEV).to(xdt)
+    ref = O.forward_f64(x.float().cpu().numpy(), cb, idx, rows, cols, deltas, b)
+    w = _weight(cb, idx, pos, vals, b)
+    y = w.matmul(x, out_dtype=torch.bfloat16, force="gemm")
+    assert y.dtype == torch.bfloat16 and w.gemm_status() == 0
+    assert rel_l2(y.float().cpu().numpy(), ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("shape,M", [((18944, 3584), 512), ((3584, 18944), 512), ((512, 3584), 2048)])
+def test_gemm_full_size_against_dense(shape, M):
+    n_out, n_in = shape
+    G = 128
+    gen = torch.Generator(device=DEV).manual_seed(n_in)
+    idx = torch.randint(0, 256, (n_out, n_in), dtype=torch.uint8, device=DEV, generator=gen)
+    cb = (torch.sort(torch.randn(256, device=DEV, generator=gen)).values * 0.02).contiguous()
+    s = (1 + 0.1 * torch.randn(n_out, n_in // G, device=DEV, generator=gen)).contiguous()
+    t = (0.002 * torch.randn(n_out, n_in // G, device=DEV, generator=gen)).contiguous()
+    nnz = n_out * n_in // 1000
+    pos = torch.sort(torch.randperm(n_out * n_in, device=DEV, generator=gen)[:nnz]).values
+    vals = (0.1 * torch.randn(nnz, device=DEV, generator=gen)).half().float()
+    bias = torch.randn(n_out, device=DEV, generator=gen)
+    from helix_substrate_b200 import HelixLinear
+    mod = HelixLinear(n_in, n_out, cb, idx, pos, vals, bias=bias, group_scales=s, group_offsets=t, group_size=G)
+    x = torch.randn(M, n_in, device=DEV, generator=gen).bfloat16()
+    y = mod(x)
+    assert y.dtype == torch.bfloat16 and mod.packed().gemm_status() == 0
+    ref = x.double() @ mod.decode_weight().double().t() + bias.double()
+    assert rel_l2(y.double().cpu().numpy(), ref.cpu().numpy()) < TOL_BF16
