@@ -201,6 +201,14 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
             }
         }
 
+        // row pointer of the sidecar goes out first: it has landed by the time the lookups are done
+        const bool sc_owner = (a.rowptr != nullptr) && (ch == rb % a.nch) && (rb * kRows + (lane & 7) < a.out_features);
+        int sc_e0 = 0, sc_e1 = 0;
+        if (sc_owner) {
+            sc_e0 = a.rowptr[rb * kRows + (lane & 7)];
+            sc_e1 = a.rowptr[rb * kRows + (lane & 7) + 1];
+        }
+
         // ---- lookups + FMAs: acc[r*MP + m] = this lane's 16-column partial ----
         float acc[kRows * MP];
 #pragma unroll
@@ -252,9 +260,8 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         }
 
         // ---- sidecar: the four lanes holding row r each take every 4th entry ----
-        if (a.rowptr != nullptr && ch == rb % a.nch && row_ok) {
-            const int e1 = a.rowptr[row_l + 1];
-            for (int e = a.rowptr[row_l] + h_l; e < e1; e += 4) {
+        if (sc_owner) {
+            for (int e = sc_e0 + h_l; e < sc_e1; e += 4) {
                 const int c = a.cols[e];
                 const float dl = a.deltas[e];
 #pragma unroll
@@ -279,27 +286,11 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         }
         float v = acc[0];
         const bool writer = (MP == 4) ? true : (MP == 2 ? (lane < 16) : (lane < 8));
-
-        bool finalize = true;
         if (a.nch > 1) {
-            const int64_t slot = ((int64_t)rb * a.nch) * (kRows * MP) + r_l * MP + m_l;
-            if (writer) __stcg(a.partial + slot + (int64_t)ch * (kRows * MP), v);
-            __threadfence();
-            __syncwarp();
-            unsigned int old = 0;
-            if (lane == 0) old = atomicAdd(a.counters + rb, 1u);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            finalize = (old == (unsigned int)(a.nch - 1));
-            if (finalize) {
-                __threadfence();
-                v = 0.f;
-                if (writer) {
-                    for (int c = 0; c < a.nch; ++c) v += __ldcg(a.partial + slot + (int64_t)c * (kRows * MP));
-                }
-                if (lane == 0) a.counters[rb] = 0u;  // leave the workspace clean for the next call
-            }
-        }
-        if (finalize && writer && row_ok && m_l < a.M) {
+            // partial of this (row block, chunk); summed by whoever arrives last (after the loop)
+            if (writer)
+                __stcg(a.partial + ((int64_t)rb * a.nch + ch) * (kRows * MP) + r_l * MP + m_l, v);
+        } else if (writer && row_ok && m_l < a.M) {
             if (a.bias != nullptr) v += a.bias[row_l];
             store_from_f32(a.y, (int64_t)m_l * a.ldy + row_l, v, a.y_dtype);
         }
@@ -312,6 +303,45 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         if (has_b) {
             if (u + 2 < u_end) load_unit(u + 2, qa);
             process(u + 1, qb);
+        }
+    }
+
+    // ---- arrival + reduction, once per warp and off the streaming loop ----
+    // (a fence or an atomic per unit would wait for the prefetched index loads
+    // and serialise the pipeline).  Each lane announces one unit; the warp then
+    // finishes every row block for which it was the last chunk to arrive:
+    // partials are added in chunk order, so the result does not depend on timing.
+    if (a.nch > 1 && u_begin < u_end) {
+        __threadfence();
+        __syncwarp();
+        for (int64_t base = u_begin; base < u_end; base += 32) {
+            const int64_t u = base + lane;
+            bool last = false;
+            int rb = 0;
+            if (u < u_end) {
+                const int ch = (int)(u / a.nrb);
+                rb = (int)(u - (int64_t)ch * a.nrb);
+                last = atomicAdd(a.counters + rb, 1u) == (unsigned int)(a.nch - 1);
+            }
+            unsigned int todo = __ballot_sync(0xffffffffu, last);
+            if (todo != 0u) __threadfence();
+            while (todo != 0u) {
+                const int src = __ffs(todo) - 1;
+                todo &= todo - 1u;
+                const int rbf = __shfl_sync(0xffffffffu, rb, src);
+                if (lane < kRows * MP) {
+                    const float* p = a.partial + (int64_t)rbf * a.nch * (kRows * MP) + lane;
+                    float v = 0.f;
+                    for (int c = 0; c < a.nch; ++c) v += __ldcg(p + (int64_t)c * (kRows * MP));
+                    const int row = rbf * kRows + lane / MP;
+                    const int m = lane % MP;
+                    if (row < a.out_features && m < a.M) {
+                        if (a.bias != nullptr) v += a.bias[row];
+                        store_from_f32(a.y, (int64_t)m * a.ldy + row, v, a.y_dtype);
+                    }
+                }
+                if (lane == src) a.counters[rbf] = 0u;  // leave the workspace clean for the next call
+            }
         }
     }
 }

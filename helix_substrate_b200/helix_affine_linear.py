@@ -14,8 +14,12 @@ from .packed import HxqWeight
 
 
 def _int8_codebook(device=None) -> torch.Tensor:
-    # fp32 division, the same rounding as the reference's int8_vals.float() / 127.0
-    return (torch.arange(256, dtype=torch.float32, device=device) - 128.0) / 127.0
+    # IEEE fp32 division on the host, the rounding of the reference's CPU
+    # ``int8_vals.float() / 127.0`` (a device-side division by a scalar is a
+    # multiplication by the reciprocal and differs in the last bit)
+    import numpy as np
+    cb = (np.arange(256, dtype=np.float32) - np.float32(128.0)) / np.float32(127.0)
+    return torch.from_numpy(cb).to(device) if device is not None else torch.from_numpy(cb)
 
 
 class HelixAffineLinear(nn.Module):

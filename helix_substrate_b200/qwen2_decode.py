@@ -1,0 +1,211 @@
+"""Greedy decode of a Qwen2-architecture decoder whose linears are HelixLinear.
+
+This is the caller around the compressed-linear path (the reference drives HF
+models with a Python greedy loop, helix_substrate/basin_runtime.py:358-445, at
+one model() call per token): RMSNorm, RoPE, grouped-query attention over a
+static KV cache and SwiGLU in plain torch ops, every projection an HXQ product,
+and the whole one-token step replayed from a CUDA graph so that the ~200 kernel
+launches per token cost no Python time.  Tensor parallel: q/k/v/gate/up are
+column-parallel, o/down row-parallel with one all-reduce each (NCCL).
+
+Weights are random-init (N(0, 0.02)) and compressed on the GPU; lm_head and the
+embedding stay dense bf16, as in the reference's policy (tensor_policy.py:199-208).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .helix_linear import HelixLinear
+from .hxq_writer_gpu import compress_weight
+from .tp import shard_helix_linear
+
+
+@dataclass
+class Qwen2Shape:
+    hidden: int = 3584
+    inter: int = 18944
+    layers: int = 28
+    heads: int = 28
+    kv_heads: int = 4
+    head_dim: int = 128
+    vocab: int = 152064
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+
+    @staticmethod
+    def qwen25_7b() -> "Qwen2Shape":
+        return Qwen2Shape()
+
+    @staticmethod
+    def qwen25_14b() -> "Qwen2Shape":
+        return Qwen2Shape(hidden=5120, inter=13824, layers=48, heads=40, kv_heads=8)
+
+    @staticmethod
+    def tiny() -> "Qwen2Shape":
+        return Qwen2Shape(hidden=256, inter=512, layers=2, heads=4, kv_heads=2, head_dim=64, vocab=1024)
+
+
+def _hxq_linear(out_f: int, in_f: int, seed: int, device, bias: bool, group_size: int, name: str,
+                mode: Optional[str], rank: int, world: int) -> HelixLinear:
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn(out_f, in_f, device=device, generator=g) * 0.02
+    b = (torch.randn(out_f, device=device, generator=g) * 0.02) if bias else None
+    enc = compress_weight(w, percentile=99.95, group_size=group_size)
+    del w
+    mod = HelixLinear(in_f, out_f, bias=b, tensor_name=name, **enc)
+    if world > 1 and mode is not None:
+        mod = shard_helix_linear(mod, mode, rank, world).to(device)
+    return mod
+
+
+class Qwen2Layer(nn.Module):
+    def __init__(self, shp: Qwen2Shape, li: int, device, group_size: int, rank: int, world: int):
+        super().__init__()
+        H, D = shp.hidden, shp.head_dim
+        if shp.heads % world or shp.kv_heads % world:
+            raise ValueError(f"tensor-parallel {world} does not divide {shp.heads} query / {shp.kv_heads} KV heads")
+        p = f"model.layers.{li}"
+        mk = lambda o, i, k, bias, name, mode: _hxq_linear(o, i, 1000 * li + k, device, bias, group_size,
+                                                           f"{p}.{name}.weight", mode, rank, world)
+        self.q_proj = mk(shp.heads * D, H, 0, True, "self_attn.q_proj", "column")
+        self.k_proj = mk(shp.kv_heads * D, H, 1, True, "self_attn.k_proj", "column")
+        self.v_proj = mk(shp.kv_heads * D, H, 2, True, "self_attn.v_proj", "column")
+        self.o_proj = mk(H, shp.heads * D, 3, False, "self_attn.o_proj", "row")
+        self.gate_proj = mk(shp.inter, H, 4, False, "mlp.gate_proj", "column")
+        self.up_proj = mk(shp.inter, H, 5, False, "mlp.up_proj", "column")
+        self.down_proj = mk(H, shp.inter, 6, False, "mlp.down_proj", "row")
+        self.ln1 = nn.Parameter(torch.ones(H, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.ln2 = nn.Parameter(torch.ones(H, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.n_q, self.n_kv = shp.heads // world, shp.kv_heads // world
+
+
+class Qwen2HxqDecoder(nn.Module):
+    """Static-cache decoder.  ``prefill`` fills the cache from a prompt,
+    ``step`` decodes one token per sequence at ``pos`` (a device scalar)."""
+
+    def __init__(self, shp: Qwen2Shape, device, batch: int, max_len: int, group_size: int = 128,
+                 rank: int = 0, world: int = 1, group=None):
+        super().__init__()
+        self.shp, self.device, self.world, self.group = shp, device, world, group
+        self.layers = nn.ModuleList(Qwen2Layer(shp, i, device, group_size, rank, world) for i in range(shp.layers))
+        g = torch.Generator(device=device).manual_seed(7)
+        self.embed = (torch.randn(shp.vocab, shp.hidden, device=device, generator=g) * 0.02).bfloat16()
+        self.lm_head = (torch.randn(shp.vocab, shp.hidden, device=device, generator=g) * 0.02).bfloat16()
+        self.norm = torch.ones(shp.hidden, device=device, dtype=torch.bfloat16)
+        n_kv = shp.kv_heads // world
+        self.k_cache = torch.zeros(shp.layers, batch, n_kv, max_len, shp.head_dim, device=device, dtype=torch.bfloat16)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        inv = 1.0 / (shp.rope_theta ** (torch.arange(0, shp.head_dim, 2, device=device, dtype=torch.float32)
+                                        / shp.head_dim))
+        ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos = torch.cat([ang.cos(), ang.cos()], -1)
+        self.sin = torch.cat([ang.sin(), ang.sin()], -1)
+        self.max_len = max_len
+
+    def _rms(self, x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.shp.rms_eps)).to(x.dtype) * w
+
+    @staticmethod
+    def _rope(x, cos, sin):
+        x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+        return (x.float() * cos + torch.cat([-x2, x1], -1).float() * sin).to(x.dtype)
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def forward_tokens(self, ids: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor,
+                       attn_len: Optional[int]) -> torch.Tensor:
+        """ids [B, T]; positions [T] (absolute); the new K/V go to cache rows
+        ``cache_rows`` [T]; attention spans cache[:attn_len] (None = whole cache
+        with a position mask, which is what the captured one-token step uses)."""
+        B, T = ids.shape
+        D = self.shp.head_dim
+        h = self.embed[ids]
+        cos, sin = self.cos[positions][None, None], self.sin[positions][None, None]
+        for li, L in enumerate(self.layers):
+            x = self._rms(h, L.ln1)
+            q = L.q_proj(x).view(B, T, L.n_q, D).transpose(1, 2)
+            k = L.k_proj(x).view(B, T, L.n_kv, D).transpose(1, 2)
+            v = L.v_proj(x).view(B, T, L.n_kv, D).transpose(1, 2)
+            q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
+            self.k_cache[li].index_copy_(2, cache_rows, k)
+            self.v_cache[li].index_copy_(2, cache_rows, v)
+            if attn_len is None:
+                kk, vv = self.k_cache[li], self.v_cache[li]
+                mask = (torch.arange(self.max_len, device=ids.device)[None, :] <= positions[:, None])[None, None]
+            else:
+                kk, vv = self.k_cache[li][:, :, :attn_len], self.v_cache[li][:, :, :attn_len]
+                mask = (torch.arange(attn_len, device=ids.device)[None, :] <= positions[:, None])[None, None]
+            a = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask, enable_gqa=True)
+            a = a.transpose(1, 2).reshape(B, T, L.n_q * D)
+            h = h + self._allreduce(L.o_proj(a))
+            x = self._rms(h, L.ln2)
+            h = h + self._allreduce(L.down_proj(F.silu(L.gate_proj(x)) * L.up_proj(x)))
+        h = self._rms(h[:, -1], self.norm)
+        return h @ self.lm_head.t()
+
+    @torch.no_grad()
+    def prefill(self, prompt: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
+        T = prompt.shape[1]
+        logits = None
+        for a in range(0, T, chunk):
+            b = min(a + chunk, T)
+            pos = torch.arange(a, b, device=prompt.device)
+            logits = self.forward_tokens(prompt[:, a:b], pos, pos, b)
+        return logits.argmax(-1)
+
+    @torch.no_grad()
+    def make_graphed_step(self, batch: int):
+        """Capture the one-token step.  Returns (run, tok, pos): write the
+        current tokens into ``tok`` [B, 1] and the position into ``pos`` [1],
+        call ``run()``, read the next tokens from its result."""
+        tok = torch.zeros(batch, 1, device=self.device, dtype=torch.long)
+        pos = torch.zeros(1, device=self.device, dtype=torch.long)
+
+        def body():
+            return self.forward_tokens(tok, pos, pos, None).argmax(-1)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                body()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = body()
+
+        def run():
+            graph.replay()
+            return out
+        return run, tok, pos
+
+    @torch.no_grad()
+    def greedy_decode(self, prompt: torch.Tensor, new_tokens: int, graphed: bool = True):
+        """Prefill, then ``new_tokens`` greedy steps.  Returns the generated
+        ids [B, new_tokens] (device tensor)."""
+        B, T = prompt.shape
+        nxt = self.prefill(prompt)
+        outs = [nxt]
+        if graphed:
+            run, tok, pos = self.make_graphed_step(B)
+        for i in range(new_tokens - 1):
+            p = T + i
+            if graphed:
+                tok.copy_(nxt[:, None])
+                pos.fill_(p)
+                nxt = run().clone()
+            else:
+                pt = torch.tensor([p], device=prompt.device)
+                nxt = self.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
+            outs.append(nxt)
+        return torch.stack(outs, 1)
