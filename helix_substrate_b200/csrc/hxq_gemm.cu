@@ -424,7 +424,15 @@ extern "C" int hxq_gemm(const hxq_desc* d, const void* x, int x_dtype, int32_t M
     if (ldx < d->in_features || ldy < d->out_features) return HXQ_E_SHAPE;
     if (d->rowptr && !d->deltas) return HXQ_E_ARG;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (!gemm::fast_ok(d))  // ragged or unaligned shapes: token groups through the decode kernels
+    if (!gemm::fast_ok(d)) {
+        // ragged or unaligned shapes: token groups through the decode kernels, which need
+        // zeroed arrival counters while this entry point's workspace may be dirty
+        const size_t need = gemv_workspace_bytes(d, 4);
+        if (need > 0) {
+            if (!workspace || workspace_bytes < need) return HXQ_E_WORKSPACE;
+            if (cudaMemsetAsync(workspace, 0, need, stream) != cudaSuccess) return HXQ_E_LAUNCH;
+        }
         return gemv_any_m(d, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
+    }
     return gemm::run(d, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, status_word, stream);
 }

@@ -36,6 +36,7 @@ namespace hxq {
 constexpr int kRows = 8;          // rows per unit
 constexpr int kChunk = 512;       // columns per unit (32 lanes x 16)
 constexpr int kLutBytes = 256 * 256;
+constexpr int kGemvSmemBytes = 2 * kLutBytes;  // the table sits on a 64 KB boundary inside this window
 
 struct GemvArgs {
     const uint8_t* idx;
@@ -66,12 +67,6 @@ struct GemvPlan {
     int64_t units;
     size_t counter_bytes, partial_bytes;
 };
-
-__device__ __forceinline__ float lut_lookup(const char* lut, uint32_t word, uint32_t lane4, int k) {
-    // (code << 8) | lane4 : byte1 <- word.byte[k], byte0 <- lane4.byte0, bytes 2,3 <- 0
-    uint32_t off = __byte_perm(word, lane4, 0x5504u | (uint32_t)(k << 4));
-    return *reinterpret_cast<const float*>(lut + off);
-}
 
 template <int MP>
 __device__ __forceinline__ void load_x_chunk(const GemvArgs& a, int col, bool col_ok, float (&xr)[MP][16]) {
@@ -136,41 +131,97 @@ struct GemvCfg {
     static constexpr int kMaxThreads = (MP == 1) ? 512 : (MP == 2 ? 384 : 256);
 };
 
+// What a warp fetches one unit ahead of consuming it.
+struct UnitPrefetch {
+    uint4 q[kRows];   // 16 index bytes per row for this lane
+    float s, t;       // group scale / offset of (row lane&7, 128-column span lane>>3)
+    int e0, e1;       // sidecar entries of row lane&7 when this unit carries the row block's sidecar
+};
+
+// One codebook lookup: the byte permute builds the ABSOLUTE shared address
+// lut_base | code << 8 | lane << 2 (lut_base is a multiple of 64 KB), so the
+// inner loop per weight is exactly PRMT, LDS, FFMA.
+__device__ __forceinline__ float lut_at(uint32_t word, uint32_t lane_key, int k) {
+    const uint32_t addr = __byte_perm(word, lane_key, 0x7604u | (uint32_t)(k << 4));
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+
 template <int MP>
 __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const GemvArgs a) {
-    extern __shared__ __align__(256) char lut[];
+    extern __shared__ __align__(1024) char dyn_smem[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
-    const uint32_t lane4 = (uint32_t)lane << 2;
+    // table at the next 64 KB boundary of the shared window (the launch reserves 128 KB)
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(dyn_smem));
+    const uint32_t lut_base = (smem_base + 0xFFFFu) & ~0xFFFFu;
+    char* lut = dyn_smem + (lut_base - smem_base);
+    const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
 
-    const int64_t u_begin = a.units * gw / a.total_warps;
-    const int64_t u_end = a.units * (gw + 1) / a.total_warps;
+    const int n_units = (int)a.units;
+    const int u_begin = (int)((int64_t)n_units * gw / a.total_warps);
+    const int u_end = (int)((int64_t)n_units * (gw + 1) / a.total_warps);
+    const int r_l = lane & 7;    // row this lane ends up holding after the butterfly
+    const int h_l = lane >> 3;   // 128-column span of the chunk this lane belongs to
+    const bool affine = a.group_size > 0;
+    const int g_base = affine ? a.col0 / a.group_size : 0;
 
-    // Index bytes of a unit -> registers.
-    auto load_unit = [&](int64_t u, uint4 (&q)[kRows]) {
-        const int ch = (int)(u / a.nrb);
-        const int rb = (int)(u - (int64_t)ch * a.nrb);
+    auto fetch = [&](int ch, int rb, int own, UnitPrefetch& f) {
         const int col = a.kbase + ch * kChunk + lane * 16;
         const bool ok = (col >= 0) && (col < a.in_features);
+        const int row0 = rb * kRows;
+        const int rmax = a.out_features - 1 - row0;
+        const uint8_t* p = a.idx + (int64_t)row0 * a.ld_idx + col;
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            int row = rb * kRows + r;
-            row = row < a.out_features ? row : a.out_features - 1;
-            q[r] = ok ? ld_stream_u4(a.idx + (int64_t)row * a.ld_idx + col) : make_uint4(0, 0, 0, 0);
+            const int rr = r < rmax ? r : rmax;   // rows past the end re-read the last row (never stored)
+            f.q[r] = ok ? ld_stream_u4(p + (int64_t)rr * a.ld_idx) : make_uint4(0, 0, 0, 0);
         }
+        const int row_l = row0 + r_l;
+        const bool row_ok = row_l < a.out_features;
+        f.s = 1.f; f.t = 0.f;
+        if (affine) {
+            const int span_col = a.kbase + ch * kChunk + h_l * 128;
+            if (span_col < a.in_features && row_ok) {
+                const int64_t o = (int64_t)row_l * a.ld_st + ((a.col0 + span_col) / a.group_size - g_base);
+                if (a.st_dtype == HXQ_F32) {
+                    f.s = reinterpret_cast<const float*>(a.scales)[o];
+                    f.t = reinterpret_cast<const float*>(a.offsets)[o];
+                } else {
+                    f.s = __half2float(reinterpret_cast<const __half*>(a.scales)[o]);
+                    f.t = __half2float(reinterpret_cast<const __half*>(a.offsets)[o]);
+                }
+            }
+        }
+        f.e0 = 0; f.e1 = 0;
+        if (a.rowptr != nullptr && ch == own && row_ok) {
+            f.e0 = a.rowptr[row_l];
+            f.e1 = a.rowptr[row_l + 1];
+        }
+    };
+
+    // unit u = ch * nrb + rb; `own` = rb % nch is the chunk that carries the sidecar of row block rb
+    int ch = 0, rb = 0, own = 0;
+    if (u_begin < u_end) {
+        ch = u_begin / a.nrb;
+        rb = u_begin - ch * a.nrb;
+        own = rb % a.nch;
+    }
+    auto advance = [&]() {
+        ++rb; ++own;
+        if (own == a.nch) own = 0;
+        if (rb == a.nrb) { rb = 0; own = 0; ++ch; }
     };
 
     // First unit's loads go out before the table is built: the first HBM round
     // trip overlaps the set-up.
-    uint4 qa[kRows], qb[kRows];
-    if (u_begin < u_end) load_unit(u_begin, qa);
+    UnitPrefetch fa, fb;
+    if (u_begin < u_end) fetch(ch, rb, own, fa);
 
-    // Lane-replicated codebook: entry c for lane l at byte c*256 + l*4.
-    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
-        const int c = i >> 5, l = i & 31;
-        *reinterpret_cast<float*>(lut + c * 256 + l * 4) = a.cb[c];
-    }
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x)
+        *reinterpret_cast<float*>(lut + (i >> 5) * 256 + (i & 31) * 4) = a.cb[i >> 5];
     __syncthreads();
 
     float xr[MP][16];
@@ -179,48 +230,38 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
     for (int m = 0; m < MP; ++m) xsum[m] = 0.f;
     int cur_ch = -1;
 
-    auto process = [&](int64_t u, const uint4 (&q)[kRows]) {
-        const int ch = (int)(u / a.nrb);
-        const int rb = (int)(u - (int64_t)ch * a.nrb);
-        const int col = a.kbase + ch * kChunk + lane * 16;
+    auto process = [&](int pch, int prb, const UnitPrefetch& f) {
+        const int col = a.kbase + pch * kChunk + lane * 16;
         const bool col_ok = (col >= 0) && (col < a.in_features);
-        if (ch != cur_ch) {  // warp-uniform
-            cur_ch = ch;
+        if (pch != cur_ch) {  // warp-uniform
+            cur_ch = pch;
             load_x_chunk<MP>(a, col, col_ok, xr);
-            if (a.group_size > 0) {
+            if (affine) {
 #pragma unroll
                 for (int m = 0; m < MP; ++m) {
-                    float s = 0.f;
+                    float sx = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) s += xr[m][j];
-                    s += __shfl_xor_sync(0xffffffffu, s, 4);
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    xsum[m] = s;  // sum of x over this lane's 128-column span
+                    for (int j = 0; j < 16; ++j) sx += xr[m][j];
+                    sx += __shfl_xor_sync(0xffffffffu, sx, 4);
+                    sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+                    sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+                    xsum[m] = sx;  // sum of x over this lane's 128-column span
                 }
             }
-        }
-
-        // row pointer of the sidecar goes out first: it has landed by the time the lookups are done
-        const bool sc_owner = (a.rowptr != nullptr) && (ch == rb % a.nch) && (rb * kRows + (lane & 7) < a.out_features);
-        int sc_e0 = 0, sc_e1 = 0;
-        if (sc_owner) {
-            sc_e0 = a.rowptr[rb * kRows + (lane & 7)];
-            sc_e1 = a.rowptr[rb * kRows + (lane & 7) + 1];
         }
 
         // ---- lookups + FMAs: acc[r*MP + m] = this lane's 16-column partial ----
         float acc[kRows * MP];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            const uint32_t w[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+            const uint32_t w[4] = {f.q[r].x, f.q[r].y, f.q[r].z, f.q[r].w};
             float p0[MP], p1[MP];
 #pragma unroll
             for (int m = 0; m < MP; ++m) { p0[m] = 0.f; p1[m] = 0.f; }
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
-                const float w0 = lut_lookup(lut, w[j >> 2], lane4, j & 3);
-                const float w1 = lut_lookup(lut, w[(j + 1) >> 2], lane4, (j + 1) & 3);
+                const float w0 = lut_at(w[j >> 2], lane_key, j & 3);
+                const float w1 = lut_at(w[(j + 1) >> 2], lane_key, (j + 1) & 3);
 #pragma unroll
                 for (int m = 0; m < MP; ++m) {
                     p0[m] = fmaf(w0, xr[m][j], p0[m]);
@@ -236,38 +277,20 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         halve<kRows * MP / 2>(acc, lane, 2);
         halve<kRows * MP / 4>(acc, lane, 1);
         // now acc[0..MP) = partial of row (lane & 7) over span (lane >> 3), per token
-        const int r_l = lane & 7;
-        const int h_l = lane >> 3;
-        const int row_l = rb * kRows + r_l;
+        const int row_l = prb * kRows + r_l;
         const bool row_ok = row_l < a.out_features;
-
-        if (a.group_size > 0) {
-            const int span_col = a.kbase + ch * kChunk + h_l * 128;  // multiple of 128 in global columns
-            if (span_col < a.in_features && row_ok) {
-                const int g = (a.col0 + span_col) / a.group_size - a.col0 / a.group_size;
-                const int64_t o = (int64_t)row_l * a.ld_st + g;
-                float s, t;
-                if (a.st_dtype == HXQ_F32) {
-                    s = reinterpret_cast<const float*>(a.scales)[o];
-                    t = reinterpret_cast<const float*>(a.offsets)[o];
-                } else {
-                    s = __half2float(reinterpret_cast<const __half*>(a.scales)[o]);
-                    t = __half2float(reinterpret_cast<const __half*>(a.offsets)[o]);
-                }
+        if (affine) {
 #pragma unroll
-                for (int m = 0; m < MP; ++m) acc[m] = fmaf(s, acc[m], t * xsum[m]);
-            }
+            for (int m = 0; m < MP; ++m) acc[m] = fmaf(f.s, acc[m], f.t * xsum[m]);
         }
 
         // ---- sidecar: the four lanes holding row r each take every 4th entry ----
-        if (sc_owner) {
-            for (int e = sc_e0 + h_l; e < sc_e1; e += 4) {
-                const int c = a.cols[e];
-                const float dl = a.deltas[e];
+        for (int e = f.e0 + h_l; e < f.e1; e += 4) {
+            const int c = a.cols[e];
+            const float dl = a.deltas[e];
 #pragma unroll
-                for (int m = 0; m < MP; ++m)
-                    if (m < a.M) acc[m] = fmaf(dl, load_as_f32(a.x, (int64_t)m * a.ldx + c, a.x_dtype), acc[m]);
-            }
+            for (int m = 0; m < MP; ++m)
+                if (m < a.M) acc[m] = fmaf(dl, load_as_f32(a.x, (int64_t)m * a.ldx + c, a.x_dtype), acc[m]);
         }
 
         // ---- finish across the four spans; tokens are dealt out for MP > 1 ----
@@ -289,20 +312,24 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         if (a.nch > 1) {
             // partial of this (row block, chunk); summed by whoever arrives last (after the loop)
             if (writer)
-                __stcg(a.partial + ((int64_t)rb * a.nch + ch) * (kRows * MP) + r_l * MP + m_l, v);
+                __stcg(a.partial + ((int64_t)prb * a.nch + pch) * (kRows * MP) + r_l * MP + m_l, v);
         } else if (writer && row_ok && m_l < a.M) {
             if (a.bias != nullptr) v += a.bias[row_l];
             store_from_f32(a.y, (int64_t)m_l * a.ldy + row_l, v, a.y_dtype);
         }
     };
 
-    for (int64_t u = u_begin; u < u_end; u += 2) {
+    for (int u = u_begin; u < u_end; u += 2) {
+        const int cha = ch, rba = rb;
+        advance();
         const bool has_b = (u + 1 < u_end);
-        if (has_b) load_unit(u + 1, qb);
-        process(u, qa);
+        if (has_b) fetch(ch, rb, own, fb);
+        process(cha, rba, fa);
         if (has_b) {
-            if (u + 2 < u_end) load_unit(u + 2, qa);
-            process(u + 1, qb);
+            const int chb = ch, rbb = rb;
+            advance();
+            if (u + 2 < u_end) fetch(ch, rb, own, fa);
+            process(chb, rbb, fb);
         }
     }
 
@@ -314,21 +341,20 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
     if (a.nch > 1 && u_begin < u_end) {
         __threadfence();
         __syncwarp();
-        for (int64_t base = u_begin; base < u_end; base += 32) {
-            const int64_t u = base + lane;
+        for (int base = u_begin; base < u_end; base += 32) {
+            const int u = base + lane;
             bool last = false;
-            int rb = 0;
+            int rbu = 0;
             if (u < u_end) {
-                const int ch = (int)(u / a.nrb);
-                rb = (int)(u - (int64_t)ch * a.nrb);
-                last = atomicAdd(a.counters + rb, 1u) == (unsigned int)(a.nch - 1);
+                rbu = u % a.nrb;
+                last = atomicAdd(a.counters + rbu, 1u) == (unsigned int)(a.nch - 1);
             }
             unsigned int todo = __ballot_sync(0xffffffffu, last);
             if (todo != 0u) __threadfence();
             while (todo != 0u) {
                 const int src = __ffs(todo) - 1;
                 todo &= todo - 1u;
-                const int rbf = __shfl_sync(0xffffffffu, rb, src);
+                const int rbf = __shfl_sync(0xffffffffu, rbu, src);
                 if (lane < kRows * MP) {
                     const float* p = a.partial + (int64_t)rbf * a.nch * (kRows * MP) + lane;
                     float v = 0.f;
@@ -444,11 +470,11 @@ static int launch_fast(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(gemv_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLutBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes) != cudaSuccess)
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    gemv_kernel<MP><<<p.grid, p.warps_per_cta * 32, kLutBytes, stream>>>(a);
+    gemv_kernel<MP><<<p.grid, p.warps_per_cta * 32, kGemvSmemBytes, stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 

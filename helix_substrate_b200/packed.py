@@ -28,12 +28,14 @@ _workspaces: dict = {}
 _status_words: dict = {}
 
 
-def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
-    """Zero-initialised scratch, one per (device, stream); grown on demand.
-    The kernels leave it zeroed, so it is cleared only when (re)allocated."""
+def _workspace(device: torch.device, nbytes: int, kind: str = "gemv") -> Optional[torch.Tensor]:
+    """Scratch, one per (device, stream, kernel family); grown on demand.
+    hxq_gemv needs its workspace zeroed and leaves it zeroed, so it is cleared
+    only when (re)allocated; hxq_gemm uses its own as plain scratch (a bf16 copy
+    of the activations) and leaves it dirty - the two are never shared."""
     if nbytes == 0:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, kind)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
@@ -145,7 +147,7 @@ class HxqWeight:
                     m0 += mm
             else:
                 nb = L.hxq_gemm_workspace_bytes(C.byref(self.desc), M)
-                ws = _workspace(self.device, nb)
+                ws = _workspace(self.device, nb, "gemm")
                 sw = _status_word(self.device)
                 st = L.hxq_gemm(C.byref(self.desc), C.c_void_p(x.data_ptr()), xd, M, x.stride(0),
                                 C.c_void_p(out.data_ptr()), _dt(out.dtype), out.stride(0),

@@ -209,3 +209,83 @@ class Qwen2HxqDecoder(nn.Module):
                 nxt = self.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
             outs.append(nxt)
         return torch.stack(outs, 1)
+
+
+def main(argv=None):
+    """``python -m helix_substrate_b200.qwen2_decode --shape 7b --batch 1 --prompt 2048 --new 128``
+    (under torchrun for tensor parallel).  Prints one JSON line with decode
+    tokens/s, ms per token and the HXQ bytes streamed per token."""
+    import argparse
+    import json
+    import os
+    import time
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="7b", choices=["7b", "14b", "tiny"])
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the shape's own)")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--new", type=int, default=128)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args(argv)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    shp = {"7b": Qwen2Shape.qwen25_7b, "14b": Qwen2Shape.qwen25_14b, "tiny": Qwen2Shape.tiny}[args.shape]()
+    if args.layers:
+        shp.layers = args.layers
+    t0 = time.perf_counter()
+    model = Qwen2HxqDecoder(shp, dev, args.batch, args.prompt + args.new + 8, rank=rank, world=world)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    prompt = torch.randint(0, shp.vocab, (args.batch, args.prompt), device=dev,
+                           generator=torch.Generator(device=dev).manual_seed(0))
+    with torch.no_grad():
+        p0, p1, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        p0.record()
+        nxt = model.prefill(prompt)
+        p1.record()
+        if args.no_graph:
+            run = None
+        else:
+            run, tok, pos = model.make_graphed_step(args.batch)
+        torch.cuda.synchronize()
+        # timed decode: new-1 graph replays
+        e1.record()
+        for i in range(args.new - 1):
+            p = args.prompt + i
+            if run is not None:
+                tok.copy_(nxt[:, None])
+                pos.fill_(p)
+                nxt = run()
+            else:
+                pt = torch.tensor([p], device=dev)
+                nxt = model.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
+        e2.record()
+        torch.cuda.synchronize()
+    ms_dec = e1.elapsed_time(e2) / (args.new - 1)
+    t = torch.tensor([ms_dec], device=dev, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_dec = float(t.item())
+    hxq_bytes = sum(m.packed().algorithmic_bytes(args.batch, 2, 2) for m in model.modules()
+                    if isinstance(m, HelixLinear))
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": args.batch * 1000.0 / ms_dec, "unit": "tok/s",
+            "ms_per_token_step": ms_dec, "batch": args.batch, "prompt": args.prompt, "new_tokens": args.new,
+            "shape": args.shape, "layers": shp.layers, "n_gpus": world, "launch": "python" if run is None else "cuda_graph",
+            "hxq_algorithmic_bytes_per_step_per_gpu": hxq_bytes,
+            "hxq_GBps_per_gpu_if_all_time_were_linears": hxq_bytes / (ms_dec * 1e-3) / 1e9,
+            "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,
+            "data": "synthetic: N(0,0.02) weights, uniform random prompt ids",
+        }), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

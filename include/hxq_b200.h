@@ -123,6 +123,11 @@ int hxq_gemv(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t l
  * (helix_substrate/triton_affine_group_matmul.py:32-109).
  * status_word: device int32 the kernel sets non-zero if a bounded wait gave
  * up (the host reads it after synchronising); may be NULL.
+ * The workspace of hxq_gemm is plain scratch (a bf16 copy of x when x is not
+ * bf16 or not 16-byte aligned): it need not be zeroed and is left dirty, so it
+ * must not double as an hxq_gemv workspace.  Shapes the tensor-core kernel does
+ * not cover (ragged or unaligned) run through the decode kernels; the call
+ * clears the part of the workspace they need first.
  */
 size_t hxq_gemm_workspace_bytes(const hxq_desc* d, int32_t M);
 int hxq_gemm(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx,

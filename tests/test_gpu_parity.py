@@ -192,7 +192,7 @@ def test_workspace_is_left_clean():
     x = torch.randn(4, 2048, device=DEV)
     w.matmul(x, force="gemv")
     torch.cuda.synchronize()
-    key = (torch.device(DEV).index, torch.cuda.current_stream(torch.device(DEV)).cuda_stream)
+    key = (torch.device(DEV).index, torch.cuda.current_stream(torch.device(DEV)).cuda_stream, "gemv")
     ws = packed._workspaces[key]
     nrb = (64 + 7) // 8
     assert int(ws[:nrb * 4].view(torch.int32).abs().sum()) == 0
