@@ -9,23 +9,29 @@
 //    row, straight into registers (no shared-memory staging: the lookup traffic
 //    already needs most of the shared-memory bandwidth).  The next unit's loads
 //    are issued before the current unit is consumed (register double buffer).
-//  * Units are numbered chunk-major (all row blocks of column chunk 0, then chunk
-//    1, ...) and dealt to the warps of a persistent grid (one CTA per SM) as equal
-//    contiguous ranges, so every SM streams the same number of bytes whatever the
-//    shape, and a warp keeps its 16 activations per token in registers for many
-//    consecutive units.
+//  * Units are numbered row-block-major (unit = rowblock * nchunks + chunk) and
+//    cut into equal contiguous ranges, one per CTA of a one-CTA-per-SM grid, so
+//    every SM streams the same number of bytes whatever the shape.  Inside a CTA
+//    warp w takes units w, w + W, w + 2W, ...: at any moment the W warps read W
+//    neighbouring chunks of the same rows, i.e. one long contiguous piece of the
+//    row-major index matrix (DRAM page locality), and when W is a multiple of
+//    the chunk count a warp keeps its 16 activations per token in registers for
+//    the whole launch.
 //  * The 256-entry codebook is replicated per lane in shared memory at a 256-byte
-//    stride (entry c, lane l at byte c*256 + l*4): every lookup hits bank == lane,
-//    conflict free, and the address (c << 8) | (l << 2) is ONE byte-permute of the
-//    index word with a per-lane constant.  Inner loop per weight: PRMT, LDS, FFMA.
+//    stride on a 64 KB boundary: every lookup hits bank == lane, conflict free,
+//    and the absolute address base | code << 8 | lane << 2 is ONE byte-permute of
+//    the index word with a per-lane constant.  Per weight: PRMT, LDS, FFMA.
 //  * The group affine is applied to per-(row, group) partial sums, not to weights:
 //    sum_i x_i (c_i s + t) = s * sum_i x_i c_i + t * sum_i x_i.  Eight lanes span one
 //    128-column group, so after three exchange steps of the warp butterfly each
 //    lane holds the partial of one (row, group) and needs one s and one t.
-//  * Column chunks of one row block are summed deterministically: every unit
-//    writes its 8 x M partials to scratch, bumps an arrival counter, and the last
-//    arriver adds the partials in chunk order, adds the bias and stores y.  No
-//    float atomics, so results are bit-identical from run to run.
+//  * Chunks of one row block are summed inside the CTA through shared memory:
+//    each unit drops its 8 x M partials into a slot, bumps a shared counter, and
+//    the last warp to arrive adds the slots in chunk order.  Only a row block
+//    that straddles two CTAs' ranges (at most two per CTA) goes through global
+//    scratch and one global atomic; there too the last arriver sums the parts in
+//    fixed order.  No float atomics anywhere: results are bit-identical from run
+//    to run.
 //  * The sidecar (row-sorted CSR of deltas) of a row block is added by the unit
 //    whose chunk equals rowblock % nchunks, which spreads that work evenly.
 
@@ -36,7 +42,12 @@ namespace hxq {
 constexpr int kRows = 8;          // rows per unit
 constexpr int kChunk = 512;       // columns per unit (32 lanes x 16)
 constexpr int kLutBytes = 256 * 256;
-constexpr int kGemvSmemBytes = 2 * kLutBytes;  // the table sits on a 64 KB boundary inside this window
+constexpr int kSlotBudgetBytes = 56 * 1024;    // in-CTA reduction slots, right after the table
+constexpr int kGemvSmemBytes = 2 * kLutBytes + kSlotBudgetBytes;  // the table sits on a 64 KB boundary inside this window
+
+#ifndef HXQ_GEMV_W1
+#define HXQ_GEMV_W1 16      // max warps per CTA at one token per launch
+#endif
 
 struct GemvArgs {
     const uint8_t* idx;
@@ -49,24 +60,58 @@ struct GemvArgs {
     const float* bias;
     const void* x;
     void* y;
-    float* partial;
-    unsigned int* counters;
+    float* scratch;           // [nrb][max_parts][8*MP] partials of row blocks shared by several CTAs
+    unsigned int* counters;   // [nrb] arrivals of those row blocks (zero between calls)
     int64_t ld_idx, ldx, ldy;
-    int64_t units;
     int32_t out_features, in_features, col0, group_size, ld_st, st_dtype;
     int32_t x_dtype, y_dtype, x_vec;
-    int32_t M;       // tokens in this launch (<= MP)
-    int32_t kbase;   // local column of chunk 0, lane 0: -(col0 % 128)
-    int32_t nch;     // column chunks
-    int32_t nrb;     // row blocks
-    int32_t total_warps;
+    int32_t M;          // tokens in this launch (<= MP)
+    int32_t kbase;      // local column of chunk 0, lane 0: -(col0 % 128)
+    int32_t nch;        // column chunks per row block
+    int32_t nrb;        // row blocks
+    int32_t units;      // nrb * nch
+    int32_t max_parts;  // CTAs that can share one row block
+    int32_t rbl_max;    // row blocks a CTA can touch (slots in shared memory)
 };
 
 struct GemvPlan {
-    int nch, nrb, kbase, grid, warps_per_cta;
-    int64_t units;
-    size_t counter_bytes, partial_bytes;
+    int nch, nrb, kbase, grid, warps_per_cta, units, max_parts, rbl_max;
+    size_t counter_bytes, scratch_bytes;
 };
+
+template <int MP>
+struct GemvCfg {
+    static constexpr int kMaxWarps = (MP == 1) ? HXQ_GEMV_W1 : (MP == 2 ? 12 : 8);
+    static constexpr int kMaxThreads = 32 * kMaxWarps;
+};
+
+// What a warp fetches one unit ahead of consuming it.
+struct UnitPrefetch {
+    uint4 q[kRows];   // 16 index bytes per row for this lane
+    float s, t;       // group scale / offset of (row lane&7, 128-column span lane>>3)
+    int e0, e1;       // sidecar entries of row lane&7 when this unit carries the row block's sidecar
+};
+
+// One codebook lookup: the byte permute builds the ABSOLUTE shared address
+// lut_base | code << 8 | lane << 2 (lut_base is a multiple of 64 KB), so the
+// inner loop per weight is exactly PRMT, LDS, FFMA.
+__device__ __forceinline__ float lut_at(uint32_t word, uint32_t lane_key, int k) {
+    const uint32_t addr = __byte_perm(word, lane_key, 0x7604u | (uint32_t)(k << 4));
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+
+// Two neighbouring lookups of one index word as a packed pair: the two loads write the
+// halves of one 64-bit register directly (no moves before the packed FMA).
+__device__ __forceinline__ uint64_t lut_pair(uint32_t word, uint32_t lane_key, int k0) {
+    const uint32_t a0 = __byte_perm(word, lane_key, 0x7604u | (uint32_t)(k0 << 4));
+    const uint32_t a1 = __byte_perm(word, lane_key, 0x7604u | (uint32_t)((k0 + 1) << 4));
+    uint64_t r;
+    asm volatile("{\n\t.reg .f32 lo, hi;\n\tld.shared.f32 lo, [%1];\n\tld.shared.f32 hi, [%2];\n\t"
+                 "mov.b64 %0, {lo, hi};\n\t}" : "=l"(r) : "r"(a0), "r"(a1));
+    return r;
+}
 
 template <int MP>
 __device__ __forceinline__ void load_x_chunk(const GemvArgs& a, int col, bool col_ok, float (&xr)[MP][16]) {
@@ -126,66 +171,88 @@ __device__ __forceinline__ void halve(float* v, int lane, int off) {
     }
 }
 
-template <int MP>
-struct GemvCfg {
-    static constexpr int kMaxThreads = (MP == 1) ? 512 : (MP == 2 ? 384 : 256);
-};
+// First unit of CTA c when `units` are cut into `grid` equal contiguous ranges.
+__host__ __device__ __forceinline__ int cta_first_unit(int units, int grid, int c) {
+    return (int)((int64_t)units * c / grid);
+}
+// CTA that owns unit u under that cut.
+__device__ __forceinline__ int cta_of_unit(int units, int grid, int u) {
+    return (int)((((int64_t)u + 1) * grid + units - 1) / units) - 1;
+}
 
-// What a warp fetches one unit ahead of consuming it.
-struct UnitPrefetch {
-    uint4 q[kRows];   // 16 index bytes per row for this lane
-    float s, t;       // group scale / offset of (row lane&7, 128-column span lane>>3)
-    int e0, e1;       // sidecar entries of row lane&7 when this unit carries the row block's sidecar
-};
-
-// One codebook lookup: the byte permute builds the ABSOLUTE shared address
-// lut_base | code << 8 | lane << 2 (lut_base is a multiple of 64 KB), so the
-// inner loop per weight is exactly PRMT, LDS, FFMA.
-__device__ __forceinline__ float lut_at(uint32_t word, uint32_t lane_key, int k) {
-    const uint32_t addr = __byte_perm(word, lane_key, 0x7604u | (uint32_t)(k << 4));
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-    return v;
+// two fp32 lanes in one 64-bit register (operands of the packed fp32 FMA of sm_100)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void ffma2(uint64_t& acc, uint64_t w, uint64_t x) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(w), "l"(x));
+}
+__device__ __forceinline__ float sum2(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
 }
 
 template <int MP>
 __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(1024) char dyn_smem[];
+    constexpr int RM = kRows * MP;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int gw = blockIdx.x * (blockDim.x >> 5) + warp;
-    // table at the next 64 KB boundary of the shared window (the launch reserves 128 KB)
+    const int W = blockDim.x >> 5;
+    // codebook table at the next 64 KB boundary of the shared window, reduction slots right after it
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(dyn_smem));
     const uint32_t lut_base = (smem_base + 0xFFFFu) & ~0xFFFFu;
     char* lut = dyn_smem + (lut_base - smem_base);
     const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
+    unsigned int* cnt_s = reinterpret_cast<unsigned int*>(lut + kLutBytes);               // [rbl_max]
+    float* part_s = reinterpret_cast<float*>(lut + kLutBytes + ((a.rbl_max * 4 + 15) & ~15));  // [rbl_max][nch][RM]
 
-    const int n_units = (int)a.units;
-    const int u_begin = (int)((int64_t)n_units * gw / a.total_warps);
-    const int u_end = (int)((int64_t)n_units * (gw + 1) / a.total_warps);
+    const int nch = a.nch;
+    const int U0 = cta_first_unit(a.units, gridDim.x, blockIdx.x);
+    const int U1 = cta_first_unit(a.units, gridDim.x, blockIdx.x + 1);
+    const int rb_first = U0 / nch;
+    const bool cta_whole = (U0 - rb_first * nch == 0) && (U1 % nch == 0);   // no row block is shared with a neighbour
     const int r_l = lane & 7;    // row this lane ends up holding after the butterfly
     const int h_l = lane >> 3;   // 128-column span of the chunk this lane belongs to
     const bool affine = a.group_size > 0;
+    const bool g128 = a.group_size == 128;
     const int g_base = affine ? a.col0 / a.group_size : 0;
+    const int span0 = a.kbase + h_l * 128;                       // local column of this lane's span in chunk 0
+    const int gq0 = (a.col0 + span0) / 128 - g_base;             // its group index when groups are 128 wide
+    const int lane_col = a.kbase + lane * 16;
+    const uint32_t ld = (uint32_t)a.ld_idx;
+    // per-step advance of (row block, chunk) when the unit index grows by W
+    const int d_rb = W / nch, d_ch = W - d_rb * nch;
 
-    auto fetch = [&](int ch, int rb, int own, UnitPrefetch& f) {
-        const int col = a.kbase + ch * kChunk + lane * 16;
-        const bool ok = (col >= 0) && (col < a.in_features);
+    auto fetch = [&](int rb, int ch, int own, UnitPrefetch& f) {
         const int row0 = rb * kRows;
-        const int rmax = a.out_features - 1 - row0;
-        const uint8_t* p = a.idx + (int64_t)row0 * a.ld_idx + col;
+        const int c0 = a.kbase + ch * kChunk;                    // local column of the chunk
+        const uint8_t* p = a.idx + (uint64_t)row0 * ld + (c0 + lane * 16);
+        const bool interior = (row0 + kRows <= a.out_features) && (c0 >= 0) && (c0 + kChunk <= a.in_features);
+        if (interior) {   // warp-uniform: no clamps, no predicates
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            const int rr = r < rmax ? r : rmax;   // rows past the end re-read the last row (never stored)
-            f.q[r] = ok ? ld_stream_u4(p + (int64_t)rr * a.ld_idx) : make_uint4(0, 0, 0, 0);
+            for (int r = 0; r < kRows; ++r) f.q[r] = ld_stream_u4(p + (uint64_t)(r * ld));
+        } else {
+            const int col = c0 + lane * 16;
+            const bool ok = (col >= 0) && (col < a.in_features);
+            const int rmax = a.out_features - 1 - row0;
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                const int rr = r < rmax ? r : rmax;   // rows past the end re-read the last row (never stored)
+                f.q[r] = ok ? ld_stream_u4(p + (uint64_t)(rr * ld)) : make_uint4(0, 0, 0, 0);
+            }
         }
         const int row_l = row0 + r_l;
         const bool row_ok = row_l < a.out_features;
         f.s = 1.f; f.t = 0.f;
         if (affine) {
-            const int span_col = a.kbase + ch * kChunk + h_l * 128;
+            const int span_col = span0 + ch * kChunk;
             if (span_col < a.in_features && row_ok) {
-                const int64_t o = (int64_t)row_l * a.ld_st + ((a.col0 + span_col) / a.group_size - g_base);
+                const int g = g128 ? gq0 + ch * 4 : (a.col0 + span_col) / a.group_size - g_base;
+                const int64_t o = (int64_t)row_l * a.ld_st + g;
                 if (a.st_dtype == HXQ_F32) {
                     f.s = reinterpret_cast<const float*>(a.scales)[o];
                     f.t = reinterpret_cast<const float*>(a.offsets)[o];
@@ -196,80 +263,136 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
             }
         }
         f.e0 = 0; f.e1 = 0;
-        if (a.rowptr != nullptr && ch == own && row_ok) {
+        if (a.rowptr != nullptr && ch == own && row_ok) {   // this unit carries the row block's sidecar
             f.e0 = a.rowptr[row_l];
             f.e1 = a.rowptr[row_l + 1];
         }
     };
 
-    // unit u = ch * nrb + rb; `own` = rb % nch is the chunk that carries the sidecar of row block rb
-    int ch = 0, rb = 0, own = 0;
-    if (u_begin < u_end) {
-        ch = u_begin / a.nrb;
-        rb = u_begin - ch * a.nrb;
-        own = rb % a.nch;
-    }
-    auto advance = [&]() {
-        ++rb; ++own;
-        if (own == a.nch) own = 0;
-        if (rb == a.nrb) { rb = 0; own = 0; ++ch; }
+    // this warp's units: U0 + warp, + W, + 2W, ...   (unit = rb * nch + ch, own = rb % nch)
+    int ua = U0 + warp;
+    int rb_a = ua / nch, ch_a = ua - rb_a * nch, own_a = rb_a % nch;
+    auto step = [&](int& rb, int& ch, int& own) {
+        ch += d_ch; rb += d_rb; own += d_rb;
+        if (ch >= nch) { ch -= nch; ++rb; ++own; }
+        while (own >= nch) own -= nch;
     };
 
-    // First unit's loads go out before the table is built: the first HBM round
-    // trip overlaps the set-up.
+    // The first unit's index rows and activations go out before the table is
+    // built: the first HBM round trip overlaps the set-up.
+#ifdef HXQ_GEMV_TRACE
+    long long* trace = reinterpret_cast<long long*>(reinterpret_cast<char*>(a.counters) + (32 << 20)) +
+                       ((size_t)blockIdx.x * 32 + warp) * 16;
+    int trace_k = 0;
+    const long long t_start = clock64();
+#define HXQ_TR() do { if (lane == 0 && trace_k < 16) trace[trace_k++] = clock64() - t_start; } while (0)
+#else
+#define HXQ_TR() do {} while (0)
+#endif
+#ifdef HXQ_GEMV_TRACE2
+#define HXQ_TR2() HXQ_TR()
+#else
+#define HXQ_TR2() do {} while (0)
+#endif
     UnitPrefetch fa, fb;
-    if (u_begin < u_end) fetch(ch, rb, own, fa);
-
-    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x)
-        *reinterpret_cast<float*>(lut + (i >> 5) * 256 + (i & 31) * 4) = a.cb[i >> 5];
-    __syncthreads();
-
-    float xr[MP][16];
+    uint64_t xp[MP][8];      // activations of the current chunk, packed in pairs
     float xsum[MP];
-#pragma unroll
-    for (int m = 0; m < MP; ++m) xsum[m] = 0.f;
     int cur_ch = -1;
-
-    auto process = [&](int pch, int prb, const UnitPrefetch& f) {
-        const int col = a.kbase + pch * kChunk + lane * 16;
+    auto load_x = [&](int ch) {
+        const int col = lane_col + ch * kChunk;
         const bool col_ok = (col >= 0) && (col < a.in_features);
-        if (pch != cur_ch) {  // warp-uniform
-            cur_ch = pch;
-            load_x_chunk<MP>(a, col, col_ok, xr);
-            if (affine) {
+        float xr[MP][16];
+        load_x_chunk<MP>(a, col, col_ok, xr);
 #pragma unroll
-                for (int m = 0; m < MP; ++m) {
-                    float sx = 0.f;
+        for (int m = 0; m < MP; ++m) {
+            float sx = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) sx += xr[m][j];
-                    sx += __shfl_xor_sync(0xffffffffu, sx, 4);
-                    sx += __shfl_xor_sync(0xffffffffu, sx, 2);
-                    sx += __shfl_xor_sync(0xffffffffu, sx, 1);
-                    xsum[m] = sx;  // sum of x over this lane's 128-column span
-                }
+            for (int j = 0; j < 8; ++j) {
+                xp[m][j] = pack2(xr[m][2 * j], xr[m][2 * j + 1]);
+                sx += xr[m][2 * j] + xr[m][2 * j + 1];
             }
+            if (affine) {   // sum of x over this lane's 128-column span
+                sx += __shfl_xor_sync(0xffffffffu, sx, 4);
+                sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+                sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+            }
+            xsum[m] = sx;
         }
+        cur_ch = ch;
+    };
+    if (ua < U1) {
+        fetch(rb_a, ch_a, own_a, fa);
+        load_x(ch_a);
+    } else {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            xsum[m] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xp[m][j] = 0ull;
+        }
+    }
 
-        // ---- lookups + FMAs: acc[r*MP + m] = this lane's 16-column partial ----
+    {   // lane-replicated table: warp w fills entries [w*per, (w+1)*per): coalesced loads, then broadcasts
+        const int per = (256 + W - 1) / W;
+        const int c_end = (warp + 1) * per < 256 ? (warp + 1) * per : 256;
+        for (int c0 = warp * per; c0 < c_end; c0 += 32) {
+            const float mine = (c0 + lane < c_end) ? a.cb[c0 + lane] : 0.f;
+            for (int k = 0; k < 32 && c0 + k < c_end; ++k)
+                *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = __shfl_sync(0xffffffffu, mine, k);
+        }
+    }
+    HXQ_TR();
+    for (int i = threadIdx.x; i < a.rbl_max; i += blockDim.x) cnt_s[i] = 0u;
+    __syncthreads();
+    HXQ_TR();
+
+    auto process = [&](int prb, int pch, const UnitPrefetch& f) {
+        if (pch != cur_ch) load_x(pch);   // warp-uniform; never taken again when W is a multiple of nch
+        const int c0 = a.kbase + pch * kChunk;
+        const bool interior = (prb * kRows + kRows <= a.out_features) && (c0 >= 0) && (c0 + kChunk <= a.in_features);
+        const int col = c0 + lane * 16;
+        const bool col_ok = interior || ((col >= 0) && (col < a.in_features));
+
+        // ---- lookups + packed FMAs: acc[r*MP + m] = this lane's 16-column partial ----
+        // Four rows at a time, column pairs outermost, lookups of the next pair issued before the
+        // FMAs of the current one: every FMA finds its table value already landed.
         float acc[kRows * MP];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            const uint32_t w[4] = {f.q[r].x, f.q[r].y, f.q[r].z, f.q[r].w};
-            float p0[MP], p1[MP];
+        for (int half = 0; half < 2; ++half) {
+            uint64_t p2[4][MP];
 #pragma unroll
-            for (int m = 0; m < MP; ++m) { p0[m] = 0.f; p1[m] = 0.f; }
+            for (int r = 0; r < 4; ++r)
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-                const float w0 = lut_at(w[j >> 2], lane_key, j & 3);
-                const float w1 = lut_at(w[(j + 1) >> 2], lane_key, (j + 1) & 3);
+                for (int m = 0; m < MP; ++m) p2[r][m] = 0ull;
+            uint64_t wa[4], wb[4];
+            auto look = [&](int j, uint64_t (&wv)[4]) {
 #pragma unroll
-                for (int m = 0; m < MP; ++m) {
-                    p0[m] = fmaf(w0, xr[m][j], p0[m]);
-                    p1[m] = fmaf(w1, xr[m][j + 1], p1[m]);
+                for (int r = 0; r < 4; ++r) {
+                    const uint4 q = f.q[4 * half + r];
+                    const uint32_t word = (j >> 1) == 0 ? q.x : ((j >> 1) == 1 ? q.y : ((j >> 1) == 2 ? q.z : q.w));
+                    wv[r] = lut_pair(word, lane_key, (2 * j) & 3);
                 }
+            };
+            look(0, wa);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                look(j + 1, wb);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) ffma2(p2[r][m], wa[r], xp[m][j]);
+                if (j + 2 < 8) look(j + 2, wa);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) ffma2(p2[r][m], wb[r], xp[m][j + 1]);
             }
 #pragma unroll
-            for (int m = 0; m < MP; ++m) acc[r * MP + m] = col_ok ? (p0[m] + p1[m]) : 0.f;
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int m = 0; m < MP; ++m) acc[(4 * half + r) * MP + m] = col_ok ? sum2(p2[r][m]) : 0.f;
+            if (acc[4 * half * MP] == 1.2345e30f) acc[0] = 0.f;   // keeps the timestamp below after the half's sums
+            HXQ_TR2();
         }
 
         // ---- butterfly over the 8 lanes of a group span: rows are dealt out ----
@@ -277,8 +400,6 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         halve<kRows * MP / 2>(acc, lane, 2);
         halve<kRows * MP / 4>(acc, lane, 1);
         // now acc[0..MP) = partial of row (lane & 7) over span (lane >> 3), per token
-        const int row_l = prb * kRows + r_l;
-        const bool row_ok = row_l < a.out_features;
         if (affine) {
 #pragma unroll
             for (int m = 0; m < MP; ++m) acc[m] = fmaf(f.s, acc[m], f.t * xsum[m]);
@@ -294,82 +415,100 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         }
 
         // ---- finish across the four spans; tokens are dealt out for MP > 1 ----
-        int m_l = 0;
+        int m_i = 0;
         if (MP == 4) {
             halve<4>(acc, lane, 8);
             halve<2>(acc, lane, 16);
-            m_l = ((lane >> 3) & 1) * 2 + ((lane >> 4) & 1);
+            m_i = ((lane >> 3) & 1) * 2 + ((lane >> 4) & 1);
         } else if (MP == 2) {
             halve<2>(acc, lane, 8);
             acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 16);
-            m_l = (lane >> 3) & 1;
+            m_i = (lane >> 3) & 1;
         } else {
             acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 8);
             acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 16);
         }
         float v = acc[0];
-        const bool writer = (MP == 4) ? true : (MP == 2 ? (lane < 16) : (lane < 8));
-        if (a.nch > 1) {
-            // partial of this (row block, chunk); summed by whoever arrives last (after the loop)
-            if (writer)
-                __stcg(a.partial + ((int64_t)prb * a.nch + pch) * (kRows * MP) + r_l * MP + m_l, v);
-        } else if (writer && row_ok && m_l < a.M) {
-            if (a.bias != nullptr) v += a.bias[row_l];
-            store_from_f32(a.y, (int64_t)m_l * a.ldy + row_l, v, a.y_dtype);
+        int row_i = r_l;                                            // (row, token) this lane holds
+        bool has = (MP == 4) ? true : (MP == 2 ? (lane < 16) : (lane < 8));
+
+        // ---- sum the chunks of the row block: inside the CTA through shared memory ----
+        int lo = 0, hi = nch;                                       // this CTA's chunks of the row block: [lo, hi)
+        if (!cta_whole) {
+            const int rb_u0 = prb * nch;
+            lo = (U0 > rb_u0 ? U0 : rb_u0) - rb_u0;
+            hi = (U1 < rb_u0 + nch ? U1 : rb_u0 + nch) - rb_u0;
+        }
+        bool fin = true;                                            // warp-uniform: we finish the CTA's share
+        if (hi - lo > 1) {
+            const int rbl = prb - rb_first;
+            float* slot = part_s + rbl * (nch * RM);
+            if (has) slot[pch * RM + row_i * MP + m_i] = v;
+            __threadfence_block();
+            __syncwarp();
+            unsigned int old = 0;
+            if (lane == 0) old = atomicAdd(&cnt_s[rbl], 1u);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            fin = (old == (unsigned int)(hi - lo - 1));
+            if (fin) {      // last chunk to arrive: add the slots in chunk order, lane j owns value j
+                __threadfence_block();
+                has = lane < RM;
+                row_i = lane / MP;
+                m_i = lane % MP;
+                v = 0.f;
+                if (has)
+                    for (int c = lo; c < hi; ++c) v += slot[c * RM + lane];
+            }
+        }
+        if (!fin) return;
+
+        // ---- a row block cut by the CTA boundary: parts meet in global scratch ----
+        if (hi - lo < nch) {
+            const int rb_u0 = prb * nch;
+            const int c_first = cta_of_unit(a.units, gridDim.x, rb_u0);
+            const int n_parts = cta_of_unit(a.units, gridDim.x, rb_u0 + nch - 1) - c_first + 1;
+            float* sp = a.scratch + (int64_t)prb * a.max_parts * RM;
+            if (has) __stcg(sp + ((int)blockIdx.x - c_first) * RM + row_i * MP + m_i, v);
+            __threadfence();
+            __syncwarp();
+            unsigned int g = 0;
+            if (lane == 0) g = atomicAdd(a.counters + prb, 1u);
+            g = __shfl_sync(0xffffffffu, g, 0);
+            if (g != (unsigned int)(n_parts - 1)) return;
+            __threadfence();
+            v = 0.f;
+            if (has)
+                for (int p = 0; p < n_parts; ++p) {
+                    v += __ldcg(sp + p * RM + row_i * MP + m_i);
+                    __stcg(sp + p * RM + row_i * MP + m_i, 0.f);   // the whole workspace goes back to zero:
+                }                                                  // another shape lays it out differently
+            if (lane == 0) a.counters[prb] = 0u;
+        }
+        const int row = prb * kRows + row_i;
+        if (has && row < a.out_features && m_i < a.M) {
+            if (a.bias != nullptr) v += a.bias[row];
+            store_from_f32(a.y, (int64_t)m_i * a.ldy + row, v, a.y_dtype);
         }
     };
 
-    for (int u = u_begin; u < u_end; u += 2) {
-        const int cha = ch, rba = rb;
-        advance();
-        const bool has_b = (u + 1 < u_end);
-        if (has_b) fetch(ch, rb, own, fb);
-        process(cha, rba, fa);
-        if (has_b) {
-            const int chb = ch, rbb = rb;
-            advance();
-            if (u + 2 < u_end) fetch(ch, rb, own, fa);
-            process(chb, rbb, fb);
-        }
+    while (ua < U1) {
+        int rb_b = rb_a, ch_b = ch_a, own_b = own_a;
+        step(rb_b, ch_b, own_b);
+        const int ub = ua + W;
+        HXQ_TR2();
+        if (ub < U1) fetch(rb_b, ch_b, own_b, fb);
+        HXQ_TR2();
+        process(rb_a, ch_a, fa);
+        HXQ_TR();
+        if (ub >= U1) break;
+        rb_a = rb_b; ch_a = ch_b; own_a = own_b;
+        step(rb_a, ch_a, own_a);
+        ua = ub + W;
+        if (ua < U1) fetch(rb_a, ch_a, own_a, fa);
+        process(rb_b, ch_b, fb);
+        HXQ_TR();
     }
-
-    // ---- arrival + reduction, once per warp and off the streaming loop ----
-    // (a fence or an atomic per unit would wait for the prefetched index loads
-    // and serialise the pipeline).  Each lane announces one unit; the warp then
-    // finishes every row block for which it was the last chunk to arrive:
-    // partials are added in chunk order, so the result does not depend on timing.
-    if (a.nch > 1 && u_begin < u_end) {
-        __threadfence();
-        __syncwarp();
-        for (int base = u_begin; base < u_end; base += 32) {
-            const int u = base + lane;
-            bool last = false;
-            int rbu = 0;
-            if (u < u_end) {
-                rbu = u % a.nrb;
-                last = atomicAdd(a.counters + rbu, 1u) == (unsigned int)(a.nch - 1);
-            }
-            unsigned int todo = __ballot_sync(0xffffffffu, last);
-            if (todo != 0u) __threadfence();
-            while (todo != 0u) {
-                const int src = __ffs(todo) - 1;
-                todo &= todo - 1u;
-                const int rbf = __shfl_sync(0xffffffffu, rbu, src);
-                if (lane < kRows * MP) {
-                    const float* p = a.partial + (int64_t)rbf * a.nch * (kRows * MP) + lane;
-                    float v = 0.f;
-                    for (int c = 0; c < a.nch; ++c) v += __ldcg(p + (int64_t)c * (kRows * MP));
-                    const int row = rbf * kRows + lane / MP;
-                    const int m = lane % MP;
-                    if (row < a.out_features && m < a.M) {
-                        if (a.bias != nullptr) v += a.bias[row];
-                        store_from_f32(a.y, (int64_t)m * a.ldy + row, v, a.y_dtype);
-                    }
-                }
-                if (lane == src) a.counters[rbf] = 0u;  // leave the workspace clean for the next call
-            }
-        }
-    }
+    HXQ_TR();
 }
 
 // Any-shape fallback (ragged IN, unaligned pointers, group sizes that are not a
@@ -439,28 +578,46 @@ bool gemv_fast_ok(const hxq_desc* d) {
 
 static int mp_for(int M) { return M >= 3 ? 4 : (M == 2 ? 2 : 1); }
 
+// grid == 0 means the streaming kernel does not cover the shape (use the fallback).
 GemvPlan gemv_plan(const hxq_desc* d, int MP, int n_sm) {
     GemvPlan p;
+    const int RM = kRows * MP;
     p.kbase = -(d->col0 % 128);
     p.nch = (d->in_features - p.kbase + kChunk - 1) / kChunk;
     p.nrb = (d->out_features + kRows - 1) / kRows;
-    p.units = (int64_t)p.nch * p.nrb;
-    const int wmax = (MP == 1) ? 16 : (MP == 2 ? 12 : 8);
-    const int wmin = wmax / 2;
-    // warps per CTA: the count whose equal split of the units wastes least
-    int best_w = wmax;
-    double best_eff = -1.0;
-    for (int w = wmax; w >= wmin; --w) {
-        const int64_t tw = (int64_t)n_sm * w;
-        const int64_t per = (p.units + tw - 1) / tw;
-        const double eff = (double)p.units / (double)(per * tw);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best_w = w; }
+    p.grid = 0; p.units = 0; p.max_parts = 1; p.rbl_max = 1; p.warps_per_cta = 1;
+    p.counter_bytes = p.scratch_bytes = 0;
+    const int64_t units64 = (int64_t)p.nch * p.nrb;
+    if (units64 > 0x3fffffffLL) return p;
+    p.units = (int)units64;
+    // one CTA per SM; more (whole multiples) only when a CTA's reduction slots would not fit
+    int grid = p.units < n_sm ? p.units : n_sm;
+    for (;;) {
+        const int upc_max = (p.units + grid - 1) / grid;
+        p.rbl_max = (upc_max - 1) / p.nch + 2;
+        const int64_t bytes = (((int64_t)p.rbl_max * 4 + 15) & ~15LL) + (int64_t)p.rbl_max * p.nch * RM * 4;
+        if (bytes <= kSlotBudgetBytes) break;
+        if (grid >= p.units) return p;
+        grid = grid + n_sm < p.units ? grid + n_sm : p.units;
     }
-    p.warps_per_cta = best_w;
-    int64_t ctas = (p.units + best_w - 1) / best_w;
-    p.grid = (int)(ctas < n_sm ? ctas : n_sm);
+    p.grid = grid;
+    const int upc_max = (p.units + grid - 1) / grid;
+    const int upc_min = p.units / grid;
+    p.max_parts = (p.nch - 1) / (upc_min > 0 ? upc_min : 1) + 2;
+    // warps per CTA: least idle slots in the CTA's last round; prefer a count that keeps each
+    // warp on one chunk (activations stay in registers), then the larger count
+    const int wmax = (MP == 1) ? GemvCfg<1>::kMaxWarps : (MP == 2 ? GemvCfg<2>::kMaxWarps : GemvCfg<4>::kMaxWarps);
+    const int wmin = wmax / 2 > 0 ? wmax / 2 : 1;
+    double best = -1.0;
+    p.warps_per_cta = wmax;
+    for (int w = wmax; w >= wmin; --w) {
+        const int rounds = (upc_max + w - 1) / w;
+        double score = (double)upc_max / ((double)rounds * w) * ((double)w / wmax > 0.8 ? 1.0 : 0.9);
+        if (w % p.nch != 0) score *= 0.97;
+        if (score > best + 1e-9) { best = score; p.warps_per_cta = w; }
+    }
     p.counter_bytes = (((size_t)p.nrb * sizeof(unsigned int)) + 255) & ~(size_t)255;
-    p.partial_bytes = (p.nch > 1) ? (size_t)p.units * kRows * MP * sizeof(float) : 0;
+    p.scratch_bytes = (p.nch > 1) ? (size_t)p.nrb * p.max_parts * RM * sizeof(float) : 0;
     return p;
 }
 
@@ -489,34 +646,34 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
     a.out_features = d->out_features; a.in_features = d->in_features; a.col0 = d->col0;
     a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
-    a.partial = nullptr; a.counters = nullptr;
-    a.units = 0; a.kbase = 0; a.nch = 1; a.nrb = 0; a.total_warps = 1; a.x_vec = 0;
+    a.scratch = nullptr; a.counters = nullptr;
+    a.units = 0; a.kbase = 0; a.nch = 1; a.nrb = 0; a.max_parts = 1; a.rbl_max = 1; a.x_vec = 0;
     const int xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
 
-    if (!gemv_fast_ok(d)) {
+    const int n_sm = sm_count();
+    if (!gemv_fast_ok(d) || gemv_plan(d, 4, n_sm).grid == 0) {
         a.x = x; a.y = y; a.M = M;
         const int blocks = (d->out_features * 32 + 255) / 256;
         gemv_generic_kernel<<<blocks, 256, 0, stream>>>(a);
         return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
     }
 
-    const int n_sm = sm_count();
     for (int m0 = 0; m0 < M;) {
         const int rem = M - m0;
         const int MP = mp_for(rem);
         const int mm = rem < MP ? rem : MP;
         const GemvPlan p = gemv_plan(d, MP, n_sm);
         if (p.nch > 1) {
-            if (!workspace || workspace_bytes < p.counter_bytes + p.partial_bytes) return HXQ_E_WORKSPACE;
+            if (!workspace || workspace_bytes < p.counter_bytes + p.scratch_bytes) return HXQ_E_WORKSPACE;
             if (!aligned_to(workspace, 16)) return HXQ_E_ALIGN;
             a.counters = reinterpret_cast<unsigned int*>(workspace);
-            a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + p.counter_bytes);
+            a.scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + p.counter_bytes);
         }
         a.x = reinterpret_cast<const char*>(x) + (int64_t)m0 * ldx * xs;
         a.y = reinterpret_cast<char*>(y) + (int64_t)m0 * ldy * ys;
         a.M = mm;
         a.kbase = p.kbase; a.nch = p.nch; a.nrb = p.nrb; a.units = p.units;
-        a.total_warps = p.grid * p.warps_per_cta;
+        a.max_parts = p.max_parts; a.rbl_max = p.rbl_max;
         a.x_vec = (aligned_to(a.x, 16) && ((ldx * xs) % 16 == 0)) ? 1 : 0;
         int st;
         if (MP == 1) st = launch_fast<1>(a, p, stream);
@@ -530,9 +687,9 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
 
 size_t gemv_workspace_bytes(const hxq_desc* d, int32_t M) {
     if (!gemv_fast_ok(d)) return 0;
-    const GemvPlan p = gemv_plan(d, M >= 3 ? 4 : (M == 2 ? 2 : 1), sm_count());
     // a call with M >= 3 may end with a 1- or 2-token launch: those need less
-    return p.nch > 1 ? p.counter_bytes + p.partial_bytes : 0;
+    const GemvPlan p = gemv_plan(d, mp_for(M), sm_count());
+    return (p.grid > 0 && p.nch > 1) ? p.counter_bytes + p.scratch_bytes : 0;
 }
 
 }  // namespace hxq

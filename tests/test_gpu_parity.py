@@ -194,8 +194,23 @@ def test_workspace_is_left_clean():
     torch.cuda.synchronize()
     key = (torch.device(DEV).index, torch.cuda.current_stream(torch.device(DEV)).cuda_stream, "gemv")
     ws = packed._workspaces[key]
-    nrb = (64 + 7) // 8
-    assert int(ws[:nrb * 4].view(torch.int32).abs().sum()) == 0
+    assert int(ws.view(torch.int32).abs().sum()) == 0, "counters and scratch must both be back to zero"
+
+
+def test_workspace_survives_a_change_of_shape():
+    """Two shapes lay counters and scratch out differently inside the same
+    workspace; the second must not see leftovers of the first."""
+    rng = np.random.default_rng(4)
+    outs = []
+    for (n_out, n_in) in ((24, 4096), (520, 1536), (24, 4096)):
+        cb, idx, pos, vals, b, s, t = _make(np.random.default_rng(n_out), n_out, n_in, 128)
+        rows, cols, deltas = O.derive_sidecar(cb, idx, pos, vals, s, t, 128)
+        x = np.random.default_rng(1).standard_normal((2, n_in)).astype(np.float32)
+        ref = O.forward_f64(x, cb, idx, rows, cols, deltas, b, s, t, 128)
+        y = _weight(cb, idx, pos, vals, b, s, t, 128).matmul(_t(x), force="gemv")
+        assert rel_l2(y.cpu().numpy(), ref) < TOL_F32
+        outs.append(y)
+    assert torch.equal(outs[0], outs[2])
 
 
 # --------------------------------------------------------------------------- full size, property based
