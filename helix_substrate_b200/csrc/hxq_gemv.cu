@@ -713,3 +713,51 @@ extern "C" int hxq_gemv(const hxq_desc* d, const void* x, int x_dtype, int32_t M
     return gemv_any_m(d, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
                       reinterpret_cast<cudaStream_t>(stream));
 }
+
+// ---- hxq_gemv_static: the decode product for callers that must not allocate -------------
+//
+// Some hosts hand every byte of device memory to their own pool at start-up, or sit inside
+// a region where the CUDA allocator may not be called at all (a serving loop with a frozen
+// memory plan, a plug-in that is only ever given input and output buffers).  They cannot
+// provide the scratch buffer hxq_gemv asks for.  This entry point keeps that scratch inside
+// the library instead: a fixed array in device memory that exists once per GPU from the
+// moment the library is loaded until the process exits.
+//
+// The array's name is only a host-side handle; the device address comes from
+// cudaGetSymbolAddress, looked up once per device (with that device current) on the first
+// call and cached.  All calls on a GPU share the one array and it keeps whatever the last
+// call left there, so the part this call needs is cleared on the stream first; two calls
+// that can run at the same time on one GPU would trample each other's partial sums.
+namespace hxq {
+
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[HXQ_GEMV_STATIC_SCRATCH_BYTES];
+static void* g_gemv_static_ptr[64] = {nullptr};
+
+}  // namespace hxq
+
+extern "C" int hxq_gemv_static(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, void* y,
+                               int y_dtype, int64_t ldy, hxq_stream_t stream_) {
+    using namespace hxq;
+    int st = validate_desc(d);
+    if (st != HXQ_OK) return st;
+    if (!x || !y) return HXQ_E_ARG;
+    if (M <= 0 || M > 16) return HXQ_E_ARG;
+    if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return HXQ_E_DTYPE;
+    if (ldx < d->in_features || ldy < d->out_features) return HXQ_E_SHAPE;
+    if (d->rowptr && !d->deltas) return HXQ_E_ARG;
+    // size check first: nothing is touched or launched for a shape the fixed array cannot serve
+    const size_t need = gemv_workspace_bytes(d, M);
+    if (need > (size_t)HXQ_GEMV_STATIC_SCRATCH_BYTES) return HXQ_E_WORKSPACE;
+
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HXQ_E_DEVICE;
+    if (g_gemv_static_ptr[dev] == nullptr) {   // first call on this device (not inside a stream capture)
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_gemv_static_scratch) != cudaSuccess || p == nullptr) return HXQ_E_DEVICE;
+        g_gemv_static_ptr[dev] = p;
+    }
+    void* scratch = g_gemv_static_ptr[dev];
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (need > 0 && cudaMemsetAsync(scratch, 0, need, stream) != cudaSuccess) return HXQ_E_LAUNCH;
+    return gemv_any_m(d, x, x_dtype, M, ldx, y, y_dtype, ldy, scratch, (size_t)HXQ_GEMV_STATIC_SCRATCH_BYTES, stream);
+}

@@ -114,6 +114,29 @@ int hxq_gemv(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t l
              void* workspace, size_t workspace_bytes, hxq_stream_t stream);
 
 /*
+ * hxq_gemv without a caller-provided workspace (no counterpart in the reference:
+ * its operators allocate freely through torch).  For hosts that may not call
+ * the CUDA allocator where they run the product - a serving process that gave
+ * all device memory to its own pool at start-up, a plug-in that only ever
+ * receives input and output buffers.  The scratch is an array of
+ * HXQ_GEMV_STATIC_SCRATCH_BYTES inside the library, present once on every GPU
+ * that loads it, for as long as the process lives.
+ *   - Shapes whose scratch need (hxq_gemv_workspace_bytes) exceeds that size are
+ *     refused with HXQ_E_WORKSPACE before anything is launched.  2 MiB covers
+ *     every Qwen2.5-7B/14B projection at M <= 16.
+ *   - The first call on a device looks the array's device address up
+ *     (cudaGetSymbolAddress); make that call once outside any stream capture.
+ *   - All calls on one GPU share the array; it is cleared on the stream as far
+ *     as the call needs it, so calls that can overlap on the GPU must not both
+ *     use this entry point (use hxq_gemv with separate workspaces there).
+ *   - Nothing is allocated or freed, by this library or by anything it calls.
+ * Same arguments and result as hxq_gemv otherwise.
+ */
+#define HXQ_GEMV_STATIC_SCRATCH_BYTES (2u << 20)
+int hxq_gemv_static(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx,
+                    void* y, int y_dtype, int64_t ldy, hxq_stream_t stream);
+
+/*
  * Prefill-time product for any M (meant for M >= 17):  same contract as
  * hxq_gemv but weights are dequantised to bf16 tiles in shared memory and
  * contracted on the tcgen05 tensor cores with fp32 TMEM accumulators.
