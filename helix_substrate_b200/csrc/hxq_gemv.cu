@@ -280,20 +280,6 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 
     // The first unit's index rows and activations go out before the table is
     // built: the first HBM round trip overlaps the set-up.
-#ifdef HXQ_GEMV_TRACE
-    long long* trace = reinterpret_cast<long long*>(reinterpret_cast<char*>(a.counters) + (32 << 20)) +
-                       ((size_t)blockIdx.x * 32 + warp) * 16;
-    int trace_k = 0;
-    const long long t_start = clock64();
-#define HXQ_TR() do { if (lane == 0 && trace_k < 16) trace[trace_k++] = clock64() - t_start; } while (0)
-#else
-#define HXQ_TR() do {} while (0)
-#endif
-#ifdef HXQ_GEMV_TRACE2
-#define HXQ_TR2() HXQ_TR()
-#else
-#define HXQ_TR2() do {} while (0)
-#endif
     UnitPrefetch fa, fb;
     uint64_t xp[MP][8];      // activations of the current chunk, packed in pairs
     float xsum[MP];
@@ -341,10 +327,8 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
                 *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = __shfl_sync(0xffffffffu, mine, k);
         }
     }
-    HXQ_TR();
     for (int i = threadIdx.x; i < a.rbl_max; i += blockDim.x) cnt_s[i] = 0u;
     __syncthreads();
-    HXQ_TR();
 
     auto process = [&](int prb, int pch, const UnitPrefetch& f) {
         if (pch != cur_ch) load_x(pch);   // warp-uniform; never taken again when W is a multiple of nch
@@ -391,8 +375,6 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
             for (int r = 0; r < 4; ++r)
 #pragma unroll
                 for (int m = 0; m < MP; ++m) acc[(4 * half + r) * MP + m] = col_ok ? sum2(p2[r][m]) : 0.f;
-            if (acc[4 * half * MP] == 1.2345e30f) acc[0] = 0.f;   // keeps the timestamp below after the half's sums
-            HXQ_TR2();
         }
 
         // ---- butterfly over the 8 lanes of a group span: rows are dealt out ----
@@ -495,20 +477,15 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         int rb_b = rb_a, ch_b = ch_a, own_b = own_a;
         step(rb_b, ch_b, own_b);
         const int ub = ua + W;
-        HXQ_TR2();
         if (ub < U1) fetch(rb_b, ch_b, own_b, fb);
-        HXQ_TR2();
         process(rb_a, ch_a, fa);
-        HXQ_TR();
         if (ub >= U1) break;
         rb_a = rb_b; ch_a = ch_b; own_a = own_b;
         step(rb_a, ch_a, own_a);
         ua = ub + W;
         if (ua < U1) fetch(rb_a, ch_a, own_a, fa);
         process(rb_b, ch_b, fb);
-        HXQ_TR();
     }
-    HXQ_TR();
 }
 
 // Any-shape fallback (ragged IN, unaligned pointers, group sizes that are not a
