@@ -306,18 +306,10 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         }
         cur_ch = ch;
     };
-    if (ua < U1) {
-        fetch(rb_a, ch_a, own_a, fa);
-        load_x(ch_a);
-    } else {
-#pragma unroll
-        for (int m = 0; m < MP; ++m) {
-            xsum[m] = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) xp[m][j] = 0ull;
-        }
-    }
-
+    // Programmatic dependent launch: the next kernel in the stream may start its own
+    // set-up as soon as every CTA of this one has got here ...
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (ua < U1) fetch(rb_a, ch_a, own_a, fa);   // weights only: nothing an earlier kernel could still be writing
     {   // lane-replicated table: warp w fills entries [w*per, (w+1)*per): coalesced loads, then broadcasts
         const int per = (256 + W - 1) / W;
         const int c_end = (warp + 1) * per < 256 ? (warp + 1) * per : 256;
@@ -328,6 +320,20 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         }
     }
     for (int i = threadIdx.x; i < a.rbl_max; i += blockDim.x) cnt_s[i] = 0u;
+    // ... and this one reads activations / touches y and the workspace only after everything
+    // before it in the stream has finished (the table and the first index rows above did
+    // not have to wait).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (ua < U1) {
+        load_x(ch_a);
+    } else {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            xsum[m] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xp[m][j] = 0ull;
+        }
+    }
     __syncthreads();
 
     auto process = [&](int prb, int pch, const UnitPrefetch& f) {
@@ -608,8 +614,17 @@ static int launch_fast(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    gemv_kernel<MP><<<p.grid, p.warps_per_cta * 32, kGemvSmemBytes, stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(p.warps_per_cta * 32);
+    cfg.dynamicSmemBytes = kGemvSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up may overlap the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a) == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
 // Shared by hxq_gemv and (until M is large enough for the tensor-core kernel)
