@@ -332,15 +332,15 @@ def main():
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
-        if K * ms < 400:  # keep the sampler alive long enough to see clocks under load
-            t_end = time.perf_counter() + 0.5
-            while time.perf_counter() < t_end:
-                run()
-            torch.cuda.synchronize()
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / K
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item()) / K
+        # keep the sampler alive long enough to see clocks under load; the number of extra passes is
+        # derived from the rank-agreed time so that every rank issues the same collectives
+        for _ in range(min(2000, int(500.0 / max(ms_step, 1e-3))) if K * ms_step < 400 else 0):
+            run()
+        torch.cuda.synchronize()
 
     # ---- end to end through the module API with host buffers ----
     # The public call (HelixLinear.forward per linear) with the step's activations
