@@ -399,8 +399,7 @@ def main():
         dist.all_reduce(nb)
     nbytes = float(nb.item())
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        _leave(world)
         return
 
     peak, peak_kind = _peaks()
@@ -435,8 +434,23 @@ def main():
         cpu = cpu_forward_sample(seconds_target=12.0)
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    _leave(world)
+
+
+def _leave(world: int) -> None:
+    """End a multi-rank run.  Tearing the NCCL process group down while CUDA graphs
+    that captured its collectives are still alive blocks for ever in this torch /
+    NCCL pairing, so ranks meet at a last barrier, flush and exit without the teardown."""
+    if world <= 1:
+        return
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -283,8 +283,12 @@ def main(argv=None):
             "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,
             "data": "synthetic: N(0,0.02) weights, uniform random prompt ids",
         }), flush=True)
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    if world > 1:   # no process-group teardown while graphs holding its collectives are alive (it blocks)
+        import sys
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
