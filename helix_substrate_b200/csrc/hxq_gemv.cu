@@ -72,6 +72,7 @@ struct GemvArgs {
     int32_t units;      // nrb * nch
     int32_t max_parts;  // CTAs that can share one row block
     int32_t rbl_max;    // row blocks a CTA can touch (slots in shared memory)
+    int32_t slot_bytes; // lean kernel: bytes of reduction slots after the table (multiple of 128)
 };
 
 struct GemvPlan {
@@ -494,6 +495,294 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
     }
 }
 
+// ---- lean kernel: shapes where every unit is whole ---------------------------------------
+//
+// OUT % 8 == 0, IN % 512 == 0, no column offset inside a group, group size 0 or 128, 16-byte
+// aligned activations: no unit touches an edge, so the per-unit code carries no bounds logic
+// at all.  Same unit, table and butterfly as gemv_kernel; what differs is the bookkeeping:
+//  * index bytes travel global -> shared with 16-byte asynchronous copies (each lane copies, and
+//    later reads back, its own 16 bytes of each of the 8 rows: a per-warp double buffer of two
+//    4 KB units that needs no synchronisation beyond the copy-group wait).  Register loads for
+//    the same bytes measured 5 us slower per launch: outstanding register loads and the table
+//    lookups then wait on one another, while asynchronous copies leave the lookups alone.
+//    Half as many registers hold index bytes, which is what lets 16 warps run unspilled,
+//  * the walk over a warp's units is incremental (one 64-bit pointer, one scale offset, one
+//    slot offset, each advanced by a warp-uniform delta),
+//  * a unit ends with ONE store of its 8 x M partial sums into its own shared-memory slot;
+//    there are no arrival counters inside the CTA.  After the last unit the CTA meets at one
+//    barrier and the warps add the slots of each row block in chunk order (deterministic),
+//    then store y - or, for a row block cut by the CTA boundary, go through the same global
+//    scratch + arrival counter as gemv_kernel.
+constexpr int kLeanSmemBytes = 232448;          // all of the SM's shared memory: table + slots + index rings
+constexpr int kRingBytesPerWarp = 2 * kRows * kChunk;   // two units
+
+struct LeanFetch {
+    float s, t;       // group scale / offset of (row lane&7, 128-column span lane>>3)
+    int e0, e1;       // sidecar entries of row lane&7 when this unit carries the row block's sidecar
+};
+
+__device__ __forceinline__ uint64_t fmul2(uint64_t w, uint64_t x) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(w), "l"(x));
+    return r;
+}
+
+template <int MP>
+__global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(const GemvArgs a) {
+    extern __shared__ __align__(1024) char dyn_smem[];
+    constexpr int RM = kRows * MP;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int W = blockDim.x >> 5;
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(dyn_smem));
+    const uint32_t lut_base = (smem_base + 0xFFFFu) & ~0xFFFFu;
+    char* lut = dyn_smem + (lut_base - smem_base);
+    const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
+    float* part_s = reinterpret_cast<float*>(lut + kLutBytes);   // [unit - S0][RM]
+    // index rings: as many warps as fit below the table, the rest above the slots
+    uint32_t ring;
+    {
+        const uint32_t lo0 = (smem_base + 127u) & ~127u;
+        const uint32_t hi0 = lut_base + kLutBytes + (uint32_t)a.slot_bytes;
+        const uint32_t n_lo = (lut_base - lo0) / kRingBytesPerWarp;
+        ring = ((uint32_t)warp < n_lo ? lo0 + warp * kRingBytesPerWarp : hi0 + (warp - n_lo) * kRingBytesPerWarp) + lane * 16;
+    }
+
+    const int nch = a.nch;
+    const int U0 = cta_first_unit(a.units, gridDim.x, blockIdx.x);
+    const int U1 = cta_first_unit(a.units, gridDim.x, blockIdx.x + 1);
+    const int rb_first = U0 / nch;
+    const int S0 = rb_first * nch;           // first unit of the first row block this CTA touches
+    const int r_l = lane & 7;
+    const int h_l = lane >> 3;
+    const bool affine = a.group_size > 0;
+    const bool st_f32 = a.st_dtype == HXQ_F32;
+    const bool sidecar = a.rowptr != nullptr;
+    const uint32_t ld = (uint32_t)a.ld_idx;
+    const int d_rb = W / nch, d_ch = W - d_rb * nch;
+    int cmask = 1;                            // the unit with chunk == rowblock & cmask carries the sidecar
+    while (cmask * 2 <= nch) cmask *= 2;
+    cmask -= 1;
+
+    // walking state: the unit about to be fetched
+    int u = U0 + warp;
+    int rb = u / nch, ch = u - rb * nch;
+    const uint8_t* p = a.idx + (uint64_t)rb * (8ull * ld) + (uint32_t)(ch * kChunk + lane * 16);
+    int so = (rb * kRows + r_l) * a.ld_st + ch * 4 + h_l;
+    const uint64_t dp_main = (uint64_t)d_rb * (8ull * ld) + (uint64_t)(d_ch * kChunk);
+    const uint64_t dp_wrap = 8ull * ld - (uint64_t)(nch * kChunk);
+    const int ds_main = d_rb * kRows * a.ld_st + d_ch * 4;
+    const int ds_wrap = kRows * a.ld_st - nch * 4;
+    const int n_my = (u < U1) ? (U1 - u + W - 1) / W : 0;
+
+    auto fetch = [&](LeanFetch& f, int buf) {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                         :: "r"(ring + buf * (kRows * kChunk) + r * kChunk), "l"(p + (uint64_t)ld * (uint32_t)r) : "memory");
+        f.s = 1.f; f.t = 0.f;
+        if (affine) {
+            if (st_f32) {
+                f.s = reinterpret_cast<const float*>(a.scales)[so];
+                f.t = reinterpret_cast<const float*>(a.offsets)[so];
+            } else {
+                f.s = __half2float(reinterpret_cast<const __half*>(a.scales)[so]);
+                f.t = __half2float(reinterpret_cast<const __half*>(a.offsets)[so]);
+            }
+        }
+        f.e0 = 0; f.e1 = 0;
+        if (sidecar && ch == (rb & cmask)) {
+            f.e0 = a.rowptr[rb * kRows + r_l];
+            f.e1 = a.rowptr[rb * kRows + r_l + 1];
+        }
+    };
+    auto advance = [&]() {
+        u += W; ch += d_ch; rb += d_rb; p += dp_main; so += ds_main;
+        if (ch >= nch) { ch -= nch; ++rb; p += dp_wrap; so += ds_wrap; }
+    };
+
+    uint64_t xp[MP][8];
+    float xsum[MP];
+    int cur_ch = -1;
+    auto load_x = [&](int c) {
+        float xr[MP][16];
+        load_x_chunk<MP>(a, c * kChunk + lane * 16, true, xr);
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            float sx = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                xp[m][j] = pack2(xr[m][2 * j], xr[m][2 * j + 1]);
+                sx += xr[m][2 * j] + xr[m][2 * j + 1];
+            }
+            if (affine) {
+                sx += __shfl_xor_sync(0xffffffffu, sx, 4);
+                sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+                sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+            }
+            xsum[m] = sx;
+        }
+        cur_ch = c;
+    };
+
+    LeanFetch fa, fb;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    int u_a = u, ch_a = ch;
+    if (n_my > 0) fetch(fa, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    {
+        const int per = (256 + W - 1) / W;
+        const int c_end = (warp + 1) * per < 256 ? (warp + 1) * per : 256;
+        for (int c0 = warp * per; c0 < c_end; c0 += 32) {
+            const float mine = (c0 + lane < c_end) ? a.cb[c0 + lane] : 0.f;
+            for (int k = 0; k < 32 && c0 + k < c_end; ++k)
+                *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = __shfl_sync(0xffffffffu, mine, k);
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (n_my > 0) {
+        load_x(ch_a);
+    } else {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            xsum[m] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xp[m][j] = 0ull;
+        }
+    }
+    __syncthreads();
+
+    auto process = [&](const LeanFetch& f, int buf, int pu, int pch) {
+        if (pch != cur_ch) load_x(pch);
+        // every copy group but the newest (the next unit) has landed
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        float acc[kRows * MP];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            uint4 qh[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(qh[r].x), "=r"(qh[r].y), "=r"(qh[r].z), "=r"(qh[r].w)
+                             : "r"(ring + buf * (kRows * kChunk) + (4 * half + r) * kChunk));
+            uint64_t p2[4][MP];
+            uint64_t wa[4], wb[4];
+            auto look = [&](int j, uint64_t (&wv)[4]) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const uint4 q = qh[r];
+                    const uint32_t word = (j >> 1) == 0 ? q.x : ((j >> 1) == 1 ? q.y : ((j >> 1) == 2 ? q.z : q.w));
+                    wv[r] = lut_pair(word, lane_key, (2 * j) & 3);
+                }
+            };
+            look(0, wa);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                look(j + 1, wb);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) {
+                        if (j == 0) p2[r][m] = fmul2(wa[r], xp[m][0]);
+                        else ffma2(p2[r][m], wa[r], xp[m][j]);
+                    }
+                if (j + 2 < 8) look(j + 2, wa);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) ffma2(p2[r][m], wb[r], xp[m][j + 1]);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int m = 0; m < MP; ++m) acc[(4 * half + r) * MP + m] = sum2(p2[r][m]);
+        }
+        halve<kRows * MP>(acc, lane, 4);
+        halve<kRows * MP / 2>(acc, lane, 2);
+        halve<kRows * MP / 4>(acc, lane, 1);
+        if (affine) {
+#pragma unroll
+            for (int m = 0; m < MP; ++m) acc[m] = fmaf(f.s, acc[m], f.t * xsum[m]);
+        }
+        for (int e = f.e0 + h_l; e < f.e1; e += 4) {
+            const int c = a.cols[e];
+            const float dl = a.deltas[e];
+#pragma unroll
+            for (int m = 0; m < MP; ++m)
+                if (m < a.M) acc[m] = fmaf(dl, load_as_f32(a.x, (int64_t)m * a.ldx + c, a.x_dtype), acc[m]);
+        }
+        int m_i = 0;
+        if (MP == 4) {
+            halve<4>(acc, lane, 8);
+            halve<2>(acc, lane, 16);
+            m_i = ((lane >> 3) & 1) * 2 + ((lane >> 4) & 1);
+        } else if (MP == 2) {
+            halve<2>(acc, lane, 8);
+            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 16);
+            m_i = (lane >> 3) & 1;
+        } else {
+            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 8);
+            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 16);
+        }
+        const bool has = (MP == 4) ? true : (MP == 2 ? (lane < 16) : (lane < 8));
+        if (has) part_s[(pu - S0) * RM + r_l * MP + m_i] = acc[0];
+    };
+
+    for (int k = 0; k < n_my; k += 2) {
+        advance();
+        const int u_b = u, ch_b = ch;
+        if (k + 1 < n_my) fetch(fb, 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per unit, empty past the end
+        process(fa, 0, u_a, ch_a);
+        if (k + 1 >= n_my) break;
+        advance();
+        u_a = u; ch_a = ch;
+        if (k + 2 < n_my) fetch(fa, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        process(fb, 1, u_b, ch_b);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // ---- add the chunks of each row block in chunk order; lane j owns value j = row * MP + token ----
+    const int rb_last = (U1 - 1) / nch;
+    const bool has = lane < RM;
+    const int row_i = lane / MP, m_i = lane % MP;
+    for (int rbx = rb_first + warp; rbx <= rb_last; rbx += W) {
+        const int rb_u0 = rbx * nch;
+        const int lo = (U0 > rb_u0 ? U0 : rb_u0) - rb_u0;
+        const int hi = (U1 < rb_u0 + nch ? U1 : rb_u0 + nch) - rb_u0;
+        float v = 0.f;
+        if (has)
+            for (int c = lo; c < hi; ++c) v += part_s[(rb_u0 + c - S0) * RM + lane];
+        if (hi - lo < nch) {   // cut by the CTA boundary: parts meet in global scratch
+            const int c_first = cta_of_unit(a.units, gridDim.x, rb_u0);
+            const int n_parts = cta_of_unit(a.units, gridDim.x, rb_u0 + nch - 1) - c_first + 1;
+            float* sp = a.scratch + (int64_t)rbx * a.max_parts * RM;
+            if (has) __stcg(sp + ((int)blockIdx.x - c_first) * RM + lane, v);
+            __threadfence();
+            __syncwarp();
+            unsigned int g = 0;
+            if (lane == 0) g = atomicAdd(a.counters + rbx, 1u);
+            g = __shfl_sync(0xffffffffu, g, 0);
+            if (g != (unsigned int)(n_parts - 1)) continue;
+            __threadfence();
+            v = 0.f;
+            if (has)
+                for (int q = 0; q < n_parts; ++q) {
+                    v += __ldcg(sp + q * RM + lane);
+                    __stcg(sp + q * RM + lane, 0.f);
+                }
+            if (lane == 0) a.counters[rbx] = 0u;
+        }
+        const int row = rbx * kRows + row_i;
+        if (has && m_i < a.M) {
+            if (a.bias != nullptr) v += a.bias[row];
+            store_from_f32(a.y, (int64_t)m_i * a.ldy + row, v, a.y_dtype);
+        }
+    }
+}
+
 // Any-shape fallback (ragged IN, unaligned pointers, group sizes that are not a
 // multiple of 128): one warp per output row, byte loads.  Correct, not fast.
 __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvArgs a) {
@@ -599,32 +888,58 @@ GemvPlan gemv_plan(const hxq_desc* d, int MP, int n_sm) {
         if (w % p.nch != 0) score *= 0.97;
         if (score > best + 1e-9) { best = score; p.warps_per_cta = w; }
     }
+#ifdef HXQ_GEMV_WFORCE
+    if (MP == 1) p.warps_per_cta = HXQ_GEMV_WFORCE;
+#endif
     p.counter_bytes = (((size_t)p.nrb * sizeof(unsigned int)) + 255) & ~(size_t)255;
     p.scratch_bytes = (p.nch > 1) ? (size_t)p.nrb * p.max_parts * RM * sizeof(float) : 0;
     return p;
 }
 
+// Shapes the lean kernel takes: every unit whole; the slots of a CTA's units and two units of
+// index bytes per warp fit beside the table.
+static int lean_slot_bytes(const GemvPlan& p, int MP) {
+    const int64_t slots = (p.units + p.grid - 1) / p.grid + p.nch - 1;
+    const int64_t b = (slots * kRows * MP * 4 + 127) & ~127LL;
+    return b > (1 << 20) ? (1 << 20) : (int)b;
+}
+static bool gemv_lean_ok(const hxq_desc* d, const GemvPlan& p, int MP, bool x_vec) {
+#ifdef HXQ_GEMV_NO_LEAN
+    return false;
+#endif
+    if (p.grid <= 0 || p.kbase != 0 || !x_vec) return false;
+    if (d->in_features % kChunk != 0 || d->out_features % kRows != 0) return false;
+    if (d->group_size != 0 && d->group_size != 128) return false;
+    if ((int64_t)d->out_features * (d->group_size ? d->ld_st : 0) > 0x7fffffffLL) return false;
+    // the table's 64 KB alignment splits the rest of the window in two: allow for one ring lost at each cut
+    const int64_t usable = (int64_t)kLeanSmemBytes - kLutBytes - lean_slot_bytes(p, MP) - 256 - 2 * kRingBytesPerWarp;
+    return (int64_t)p.warps_per_cta * kRingBytesPerWarp <= usable;
+}
+
 template <int MP>
-static int launch_fast(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream) {
+static int launch_fast(const GemvArgs& a, const GemvPlan& p, bool lean, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(gemv_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes) != cudaSuccess)
             return HXQ_E_DEVICE;
+        if (cudaFuncSetAttribute(gemv_lean_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLeanSmemBytes) != cudaSuccess)
+            return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.grid);
     cfg.blockDim = dim3(p.warps_per_cta * 32);
-    cfg.dynamicSmemBytes = kGemvSmemBytes;
+    cfg.dynamicSmemBytes = lean ? kLeanSmemBytes : kGemvSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up may overlap the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a) == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+    const cudaError_t e = lean ? cudaLaunchKernelEx(&cfg, gemv_lean_kernel<MP>, a) : cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
 // Shared by hxq_gemv and (until M is large enough for the tensor-core kernel)
@@ -639,7 +954,7 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
     a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     a.scratch = nullptr; a.counters = nullptr;
-    a.units = 0; a.kbase = 0; a.nch = 1; a.nrb = 0; a.max_parts = 1; a.rbl_max = 1; a.x_vec = 0;
+    a.units = 0; a.kbase = 0; a.nch = 1; a.nrb = 0; a.max_parts = 1; a.rbl_max = 1; a.x_vec = 0; a.slot_bytes = 0;
     const int xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
 
     const int n_sm = sm_count();
@@ -667,10 +982,12 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
         a.kbase = p.kbase; a.nch = p.nch; a.nrb = p.nrb; a.units = p.units;
         a.max_parts = p.max_parts; a.rbl_max = p.rbl_max;
         a.x_vec = (aligned_to(a.x, 16) && ((ldx * xs) % 16 == 0)) ? 1 : 0;
+        const bool lean = gemv_lean_ok(d, p, MP, a.x_vec != 0);
+        a.slot_bytes = lean ? lean_slot_bytes(p, MP) : 0;
         int st;
-        if (MP == 1) st = launch_fast<1>(a, p, stream);
-        else if (MP == 2) st = launch_fast<2>(a, p, stream);
-        else st = launch_fast<4>(a, p, stream);
+        if (MP == 1) st = launch_fast<1>(a, p, lean, stream);
+        else if (MP == 2) st = launch_fast<2>(a, p, lean, stream);
+        else st = launch_fast<4>(a, p, lean, stream);
         if (st != HXQ_OK) return st;
         m0 += mm;
     }
