@@ -506,6 +506,10 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 //    the same bytes measured 5 us slower per launch: outstanding register loads and the table
 //    lookups then wait on one another, while asynchronous copies leave the lookups alone.
 //    Half as many registers hold index bytes, which is what lets 16 warps run unspilled,
+//  * the activations of the next unit's chunk ride along in the same copy group whenever the
+//    chunk changes, and a row block's sidecar is dealt out one entry per lane over up to eight
+//    of its units, each fetching its entry's column and delta before the lookups start and the
+//    activation it meets half-way through: no load is waited for right after it is issued,
 //  * the walk over a warp's units is incremental (one 64-bit pointer, one scale offset, one
 //    slot offset, each advanced by a warp-uniform delta),
 //  * a unit ends with ONE store of its 8 x M partial sums into its own shared-memory slot;
@@ -514,11 +518,12 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 //    then store y - or, for a row block cut by the CTA boundary, go through the same global
 //    scratch + arrival counter as gemv_kernel.
 constexpr int kLeanSmemBytes = 232448;          // all of the SM's shared memory: table + slots + index rings
-constexpr int kRingBytesPerWarp = 2 * kRows * kChunk;   // two units
+constexpr int kLeanCarriers = 8;                // units of a row block that share its sidecar
 
 struct LeanFetch {
     float s, t;       // group scale / offset of (row lane&7, 128-column span lane>>3)
-    int e0, e1;       // sidecar entries of row lane&7 when this unit carries the row block's sidecar
+    int e, e1;        // this lane's sidecar entry of row lane&7 (none if e >= e1) and the row's end
+    bool last;        // this unit also walks the entries beyond kLeanCarriers * 4 per row
 };
 
 __device__ __forceinline__ uint64_t fmul2(uint64_t w, uint64_t x) {
@@ -539,15 +544,21 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     char* lut = dyn_smem + (lut_base - smem_base);
     const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
     float* part_s = reinterpret_cast<float*>(lut + kLutBytes);   // [unit - S0][RM]
-    // index rings: as many warps as fit below the table, the rest above the slots
-    uint32_t ring;
+    // staging: 2 W unit buffers of 4 KB (warp w owns 2w and 2w+1), as many as fit below the table and
+    // the rest above the slots, then one activation chunk per warp
+    const int xs_lane = (a.x_dtype == HXQ_F32) ? 64 : 32;          // bytes of one token's 16 activations
+    uint32_t ring_q0, ring_q1, ring_x;
     {
+        constexpr uint32_t kUnitBytes = kRows * kChunk;
         const uint32_t lo0 = (smem_base + 127u) & ~127u;
         const uint32_t hi0 = lut_base + kLutBytes + (uint32_t)a.slot_bytes;
-        const uint32_t n_lo = (lut_base - lo0) / kRingBytesPerWarp;
-        ring = ((uint32_t)warp < n_lo ? lo0 + warp * kRingBytesPerWarp : hi0 + (warp - n_lo) * kRingBytesPerWarp) + lane * 16;
+        const uint32_t n_lo = (lut_base - lo0) / kUnitBytes;
+        const uint32_t i0 = 2 * warp, i1 = 2 * warp + 1, n_q = 2 * W;
+        ring_q0 = (i0 < n_lo ? lo0 + i0 * kUnitBytes : hi0 + (i0 - n_lo) * kUnitBytes) + lane * 16;
+        ring_q1 = (i1 < n_lo ? lo0 + i1 * kUnitBytes : hi0 + (i1 - n_lo) * kUnitBytes) + lane * 16;
+        const uint32_t n_hi = n_q > n_lo ? n_q - n_lo : 0u;
+        ring_x = hi0 + n_hi * kUnitBytes + warp * (MP * 32 * xs_lane) + lane * xs_lane;   // token m at + m * 32 * xs_lane
     }
-
     const int nch = a.nch;
     const int U0 = cta_first_unit(a.units, gridDim.x, blockIdx.x);
     const int U1 = cta_first_unit(a.units, gridDim.x, blockIdx.x + 1);
@@ -560,13 +571,14 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     const bool sidecar = a.rowptr != nullptr;
     const uint32_t ld = (uint32_t)a.ld_idx;
     const int d_rb = W / nch, d_ch = W - d_rb * nch;
-    int cmask = 1;                            // the unit with chunk == rowblock & cmask carries the sidecar
-    while (cmask * 2 <= nch) cmask *= 2;
-    cmask -= 1;
+    // sidecar carriers of row block rb: the units with (chunk - rb) mod nch < n_car
+    const int n_car = nch < kLeanCarriers ? nch : kLeanCarriers;
+    const int own_step = d_rb % nch;
 
     // walking state: the unit about to be fetched
     int u = U0 + warp;
     int rb = u / nch, ch = u - rb * nch;
+    int own = rb % nch;
     const uint8_t* p = a.idx + (uint64_t)rb * (8ull * ld) + (uint32_t)(ch * kChunk + lane * 16);
     int so = (rb * kRows + r_l) * a.ld_st + ch * 4 + h_l;
     const uint64_t dp_main = (uint64_t)d_rb * (8ull * ld) + (uint64_t)(d_ch * kChunk);
@@ -575,11 +587,26 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     const int ds_wrap = kRows * a.ld_st - nch * 4;
     const int n_my = (u < U1) ? (U1 - u + W - 1) / W : 0;
 
-    auto fetch = [&](LeanFetch& f, int buf) {
+    auto fetch = [&](LeanFetch& f, int buf, bool with_x) {
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                         :: "r"(ring + buf * (kRows * kChunk) + r * kChunk), "l"(p + (uint64_t)ld * (uint32_t)r) : "memory");
+                         :: "r"((buf ? ring_q1 : ring_q0) + r * kChunk), "l"(p + (uint64_t)ld * (uint32_t)r) : "memory");
+        if (with_x) {   // warp-uniform: the unit's chunk differs from the one whose activations are in registers
+            const char* xg = reinterpret_cast<const char*>(a.x) + (size_t)(ch * kChunk + lane * 16) * (xs_lane >> 4);
+#pragma unroll
+            for (int m = 0; m < MP; ++m) {
+                if (m < a.M) {
+                    const char* xm = xg + (size_t)m * a.ldx * (xs_lane >> 4);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane), "l"(xm) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 16), "l"(xm + 16) : "memory");
+                    if (xs_lane == 64) {
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 32), "l"(xm + 32) : "memory");
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 48), "l"(xm + 48) : "memory");
+                    }
+                }
+            }
+        }
         f.s = 1.f; f.t = 0.f;
         if (affine) {
             if (st_f32) {
@@ -590,23 +617,27 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
                 f.t = __half2float(reinterpret_cast<const __half*>(a.offsets)[so]);
             }
         }
-        f.e0 = 0; f.e1 = 0;
-        if (sidecar && ch == (rb & cmask)) {
-            f.e0 = a.rowptr[rb * kRows + r_l];
-            f.e1 = a.rowptr[rb * kRows + r_l + 1];
+        f.e = 0; f.e1 = 0; f.last = false;
+        if (sidecar) {
+            int i = ch - own;
+            if (i < 0) i += nch;
+            if (i < n_car) {   // entry 4 i + (lane >> 3) of row lane & 7
+                f.e = a.rowptr[rb * kRows + r_l] + i * 4 + h_l;
+                f.e1 = a.rowptr[rb * kRows + r_l + 1];
+                f.last = (i == n_car - 1);
+            }
         }
     };
     auto advance = [&]() {
-        u += W; ch += d_ch; rb += d_rb; p += dp_main; so += ds_main;
-        if (ch >= nch) { ch -= nch; ++rb; p += dp_wrap; so += ds_wrap; }
+        u += W; ch += d_ch; rb += d_rb; p += dp_main; so += ds_main; own += own_step;
+        if (ch >= nch) { ch -= nch; ++rb; p += dp_wrap; so += ds_wrap; ++own; }
+        if (own >= nch) own -= nch;
     };
 
     uint64_t xp[MP][8];
     float xsum[MP];
     int cur_ch = -1;
-    auto load_x = [&](int c) {
-        float xr[MP][16];
-        load_x_chunk<MP>(a, c * kChunk + lane * 16, true, xr);
+    auto set_x = [&](float (&xr)[MP][16], int c) {
 #pragma unroll
         for (int m = 0; m < MP; ++m) {
             float sx = 0.f;
@@ -624,11 +655,49 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
         }
         cur_ch = c;
     };
+    auto load_x = [&](int c) {          // straight from global: the first unit only
+        float xr[MP][16];
+        load_x_chunk<MP>(a, c * kChunk + lane * 16, true, xr);
+        set_x(xr, c);
+    };
+    auto read_x = [&](int c) {          // from the copy a fetch left in shared memory
+        float xr[MP][16];
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            if (m >= a.M) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) xr[m][j] = 0.f;
+                continue;
+            }
+            uint32_t w[16];
+            const int nq = xs_lane >> 4;
+            for (int k = 0; k < 4; ++k) {
+                if (k < nq)
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w[4 * k]), "=r"(w[4 * k + 1]), "=r"(w[4 * k + 2]), "=r"(w[4 * k + 3])
+                                 : "r"(ring_x + m * 32 * xs_lane + 16 * k));
+            }
+            if (a.x_dtype == HXQ_F32) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) xr[m][j] = __uint_as_float(w[j]);
+            } else if (a.x_dtype == HXQ_BF16) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { xr[m][2 * j] = __uint_as_float(w[j] << 16); xr[m][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                    xr[m][2 * j] = __low2float(h); xr[m][2 * j + 1] = __high2float(h);
+                }
+            }
+        }
+        set_x(xr, c);
+    };
 
     LeanFetch fa, fb;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int u_a = u, ch_a = ch;
-    if (n_my > 0) fetch(fa, 0);
+    if (n_my > 0) fetch(fa, 0, false);   // no activations yet: an earlier kernel may still be writing them
     asm volatile("cp.async.commit_group;" ::: "memory");
     {
         const int per = (256 + W - 1) / W;
@@ -652,10 +721,13 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     }
     __syncthreads();
 
-    auto process = [&](const LeanFetch& f, int buf, int pu, int pch) {
-        if (pch != cur_ch) load_x(pch);
-        // every copy group but the newest (the next unit) has landed
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+    auto compute = [&](const LeanFetch& f, int buf, int pu) {
+        // this lane's sidecar entry: column and delta go out now, the activation it meets after the
+        // first half of the lookups, the product at the end
+        const bool sc = f.e < f.e1;
+        int sc_c = 0;
+        float sc_d = 0.f, sc_x[MP];
+        if (sc) { sc_c = a.cols[f.e]; sc_d = a.deltas[f.e]; }
         float acc[kRows * MP];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -664,7 +736,7 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
             for (int r = 0; r < 4; ++r)
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(qh[r].x), "=r"(qh[r].y), "=r"(qh[r].z), "=r"(qh[r].w)
-                             : "r"(ring + buf * (kRows * kChunk) + (4 * half + r) * kChunk));
+                             : "r"((buf ? ring_q1 : ring_q0) + (4 * half + r) * kChunk));
             uint64_t p2[4][MP];
             uint64_t wa[4], wb[4];
             auto look = [&](int j, uint64_t (&wv)[4]) {
@@ -696,6 +768,11 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
             for (int r = 0; r < 4; ++r)
 #pragma unroll
                 for (int m = 0; m < MP; ++m) acc[(4 * half + r) * MP + m] = sum2(p2[r][m]);
+            if (half == 0) {
+#pragma unroll
+                for (int m = 0; m < MP; ++m)
+                    sc_x[m] = (sc && m < a.M) ? load_as_f32(a.x, (int64_t)m * a.ldx + sc_c, a.x_dtype) : 0.f;
+            }
         }
         halve<kRows * MP>(acc, lane, 4);
         halve<kRows * MP / 2>(acc, lane, 2);
@@ -704,12 +781,16 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
 #pragma unroll
             for (int m = 0; m < MP; ++m) acc[m] = fmaf(f.s, acc[m], f.t * xsum[m]);
         }
-        for (int e = f.e0 + h_l; e < f.e1; e += 4) {
-            const int c = a.cols[e];
-            const float dl = a.deltas[e];
 #pragma unroll
-            for (int m = 0; m < MP; ++m)
-                if (m < a.M) acc[m] = fmaf(dl, load_as_f32(a.x, (int64_t)m * a.ldx + c, a.x_dtype), acc[m]);
+        for (int m = 0; m < MP; ++m) acc[m] = fmaf(sc_d, sc_x[m], acc[m]);
+        if (f.last) {   // rows with more entries than the carriers take in one go
+            for (int e = f.e + 4; e < f.e1; e += 4) {
+                const int c = a.cols[e];
+                const float dl = a.deltas[e];
+#pragma unroll
+                for (int m = 0; m < MP; ++m)
+                    if (m < a.M) acc[m] = fmaf(dl, load_as_f32(a.x, (int64_t)m * a.ldx + c, a.x_dtype), acc[m]);
+            }
         }
         int m_i = 0;
         if (MP == 4) {
@@ -729,17 +810,22 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     };
 
     for (int k = 0; k < n_my; k += 2) {
+        // unit k: index bytes in buffer 0; one copy group in flight at most, and it has to be in
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (ch_a != cur_ch) read_x(ch_a);
         advance();
         const int u_b = u, ch_b = ch;
-        if (k + 1 < n_my) fetch(fb, 1);
-        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per unit, empty past the end
-        process(fa, 0, u_a, ch_a);
+        if (k + 1 < n_my) fetch(fb, 1, ch_b != ch_a);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        compute(fa, 0, u_a);
         if (k + 1 >= n_my) break;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (ch_b != cur_ch) read_x(ch_b);
         advance();
         u_a = u; ch_a = ch;
-        if (k + 2 < n_my) fetch(fa, 0);
+        if (k + 2 < n_my) fetch(fa, 0, ch_a != ch_b);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        process(fb, 1, u_b, ch_b);
+        compute(fb, 1, u_b);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -903,17 +989,21 @@ static int lean_slot_bytes(const GemvPlan& p, int MP) {
     const int64_t b = (slots * kRows * MP * 4 + 127) & ~127LL;
     return b > (1 << 20) ? (1 << 20) : (int)b;
 }
-static bool gemv_lean_ok(const hxq_desc* d, const GemvPlan& p, int MP, bool x_vec) {
+// Most warps whose staging (two 4 KB unit buffers + one chunk of activations each) fits beside the
+// table and the slots, wherever the table's 64 KB boundary falls in the window.
+static int lean_max_warps(const GemvPlan& p, int MP, int x_dtype) {
+    const int64_t per_warp = 2 * kRows * kChunk + (int64_t)MP * kChunk * (x_dtype == HXQ_F32 ? 4 : 2);
+    const int64_t room = (int64_t)kLeanSmemBytes - kLutBytes - lean_slot_bytes(p, MP) - 256 - kRows * kChunk;
+    return room > 0 ? (int)(room / per_warp) : 0;
+}
+static bool gemv_lean_shape(const hxq_desc* d, const GemvPlan& p, bool x_vec) {
 #ifdef HXQ_GEMV_NO_LEAN
     return false;
 #endif
     if (p.grid <= 0 || p.kbase != 0 || !x_vec) return false;
     if (d->in_features % kChunk != 0 || d->out_features % kRows != 0) return false;
     if (d->group_size != 0 && d->group_size != 128) return false;
-    if ((int64_t)d->out_features * (d->group_size ? d->ld_st : 0) > 0x7fffffffLL) return false;
-    // the table's 64 KB alignment splits the rest of the window in two: allow for one ring lost at each cut
-    const int64_t usable = (int64_t)kLeanSmemBytes - kLutBytes - lean_slot_bytes(p, MP) - 256 - 2 * kRingBytesPerWarp;
-    return (int64_t)p.warps_per_cta * kRingBytesPerWarp <= usable;
+    return (int64_t)d->out_features * (d->group_size ? d->ld_st : 0) <= 0x7fffffffLL;
 }
 
 template <int MP>
@@ -982,12 +1072,18 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
         a.kbase = p.kbase; a.nch = p.nch; a.nrb = p.nrb; a.units = p.units;
         a.max_parts = p.max_parts; a.rbl_max = p.rbl_max;
         a.x_vec = (aligned_to(a.x, 16) && ((ldx * xs) % 16 == 0)) ? 1 : 0;
-        const bool lean = gemv_lean_ok(d, p, MP, a.x_vec != 0);
+        GemvPlan pl = p;
+        bool lean = gemv_lean_shape(d, p, a.x_vec != 0);
+        if (lean) {
+            const int wfit = lean_max_warps(p, MP, x_dtype);
+            if (pl.warps_per_cta > wfit) pl.warps_per_cta = wfit;
+            lean = pl.warps_per_cta >= 4;
+        }
         a.slot_bytes = lean ? lean_slot_bytes(p, MP) : 0;
         int st;
-        if (MP == 1) st = launch_fast<1>(a, p, lean, stream);
-        else if (MP == 2) st = launch_fast<2>(a, p, lean, stream);
-        else st = launch_fast<4>(a, p, lean, stream);
+        if (MP == 1) st = launch_fast<1>(a, lean ? pl : p, lean, stream);
+        else if (MP == 2) st = launch_fast<2>(a, lean ? pl : p, lean, stream);
+        else st = launch_fast<4>(a, lean ? pl : p, lean, stream);
         if (st != HXQ_OK) return st;
         m0 += mm;
     }
