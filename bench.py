@@ -425,7 +425,7 @@ def main():
         "gpu_launches": n_launch_per_step * K,
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8TBps": per_gpu / 8000.0, "traffic": None,
-                     "kernel": "hxq::gemv_kernel<1>" if M == 1 else "hxq::gemv_kernel",
+                     "kernel": "hxq::gemv_lean_kernel<1>" if M == 1 else "hxq::gemv_lean_kernel",
                      "algorithmic_bytes_per_launch": nbytes_rank / (3 * L),
                      "avg_launch_us": ms_step * 1e3 / (3 * L)},
         "clocks": clk.summary(),

@@ -35,6 +35,8 @@
 //  * The sidecar (row-sorted CSR of deltas) of a row block is added by the unit
 //    whose chunk equals rowblock % nchunks, which spreads that work evenly.
 
+#include <cuda.h>
+
 #include "hxq_common.cuh"
 
 namespace hxq {
@@ -520,6 +522,12 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 constexpr int kLeanSmemBytes = 232448;          // all of the SM's shared memory: table + slots + index rings
 constexpr int kLeanCarriers = 8;                // units of a row block that share its sidecar
 
+#ifndef HXQ_GEMV_TMA
+#define HXQ_GEMV_TMA 0     // 0: 16-byte asynchronous copies per lane; 1: one bulk tensor copy per unit, issued by one lane
+#endif                     // (same results; measured 1.4-2 us slower per launch than the per-lane copies)
+constexpr int kLeanBarBytes = 256;              // two mbarriers per warp, up to 16 warps
+__device__ int g_gemv_status = 0;               // set to HXQ_E_TIMEOUT if a bounded wait on a copy gave up
+
 struct LeanFetch {
     float s, t;       // group scale / offset of (row lane&7, 128-column span lane>>3)
     int e, e1;        // this lane's sidecar entry of row lane&7 (none if e >= e1) and the row's end
@@ -533,7 +541,8 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t w, uint64_t x) {
 }
 
 template <int MP>
-__global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1)
+gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     extern __shared__ __align__(1024) char dyn_smem[];
     constexpr int RM = kRows * MP;
     const int lane = threadIdx.x & 31;
@@ -559,6 +568,18 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
         const uint32_t n_hi = n_q > n_lo ? n_q - n_lo : 0u;
         ring_x = hi0 + n_hi * kUnitBytes + warp * (MP * 32 * xs_lane) + lane * xs_lane;   // token m at + m * 32 * xs_lane
     }
+#if HXQ_GEMV_TMA
+    // one mbarrier per unit buffer, at the end of the slot area; only this warp ever touches its two
+    const uint32_t bar0 = lut_base + kLutBytes + (uint32_t)a.slot_bytes - kLeanBarBytes + warp * 16;
+    if (lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    uint32_t phase = 0;
+    bool alive = true;      // false once a wait on a copy has given up: the warp stops issuing and computing
+#endif
     const int nch = a.nch;
     const int U0 = cta_first_unit(a.units, gridDim.x, blockIdx.x);
     const int U1 = cta_first_unit(a.units, gridDim.x, blockIdx.x + 1);
@@ -588,6 +609,24 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     const int n_my = (u < U1) ? (U1 - u + W - 1) / W : 0;
 
     auto fetch = [&](LeanFetch& f, int buf, bool with_x) {
+#if HXQ_GEMV_TMA
+        // the buffer was last read with ordinary loads: order them before the bulk copy's writes
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && alive) {
+            const uint32_t bar = bar0 + buf * 8;
+            const uint32_t xbytes = with_x ? (uint32_t)(a.M * 32 * xs_lane) : 0u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"((uint32_t)(kRows * kChunk) + xbytes) : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                         :: "r"(buf ? ring_q1 : ring_q0), "l"(reinterpret_cast<uint64_t>(&tmap)), "r"(bar), "r"(ch * (kChunk / 4)), "r"(rb * kRows) : "memory");
+            if (with_x) {
+                const char* xg = reinterpret_cast<const char*>(a.x) + (size_t)(ch * kChunk) * (xs_lane >> 4);
+                for (int m = 0; m < a.M; ++m)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 :: "r"(ring_x + m * 32 * xs_lane), "l"(xg + (size_t)m * a.ldx * (xs_lane >> 4)), "r"(32 * xs_lane), "r"(bar) : "memory");
+            }
+        }
+#else
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
@@ -607,6 +646,7 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
                 }
             }
         }
+#endif
         f.s = 1.f; f.t = 0.f;
         if (affine) {
             if (st_f32) {
@@ -698,7 +738,9 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int u_a = u, ch_a = ch;
     if (n_my > 0) fetch(fa, 0, false);   // no activations yet: an earlier kernel may still be writing them
+#if !HXQ_GEMV_TMA
     asm volatile("cp.async.commit_group;" ::: "memory");
+#endif
     {
         const int per = (256 + W - 1) / W;
         const int c_end = (warp + 1) * per < 256 ? (warp + 1) * per : 256;
@@ -809,25 +851,61 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_lean_kernel(
         if (has) part_s[(pu - S0) * RM + r_l * MP + m_i] = acc[0];
     };
 
+#if HXQ_GEMV_TMA
+    // Bounded wait for the copies of one buffer; a warp that gives up raises the status word, lets
+    // what it has in flight land (second, shorter wait) and does no more work.
+    auto landed = [&](int buf) {
+        if (!alive) return;
+        const uint32_t bar = bar0 + buf * 8;
+        uint32_t ok = 0;
+        const long long t0 = clock64();
+        for (;;) {
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(bar), "r"(phase) : "memory");
+            if (ok) return;
+            if (clock64() - t0 > 2000000000LL) break;
+        }
+        alive = false;
+        if (lane == 0) atomicExch(&g_gemv_status, HXQ_E_TIMEOUT);
+    };
+#define HXQ_LEAN_COMMIT()
+#define HXQ_LEAN_LANDED(buf) landed(buf)
+#else
+#define HXQ_LEAN_COMMIT() asm volatile("cp.async.commit_group;" ::: "memory")   /* one group per unit, empty past the end */
+#define HXQ_LEAN_LANDED(buf) asm volatile("cp.async.wait_group 0;" ::: "memory")
+    const bool alive = true;
+#endif
     for (int k = 0; k < n_my; k += 2) {
-        // unit k: index bytes in buffer 0; one copy group in flight at most, and it has to be in
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (ch_a != cur_ch) read_x(ch_a);
+        // unit k: index bytes in buffer 0; one unit's copies in flight at most, and they have to be in
+        HXQ_LEAN_LANDED(0);
+        if (alive && ch_a != cur_ch) read_x(ch_a);
         advance();
         const int u_b = u, ch_b = ch;
         if (k + 1 < n_my) fetch(fb, 1, ch_b != ch_a);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        compute(fa, 0, u_a);
+        HXQ_LEAN_COMMIT();
+        if (alive) compute(fa, 0, u_a);
         if (k + 1 >= n_my) break;
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (ch_b != cur_ch) read_x(ch_b);
+        HXQ_LEAN_LANDED(1);
+        if (alive && ch_b != cur_ch) read_x(ch_b);
         advance();
         u_a = u; ch_a = ch;
         if (k + 2 < n_my) fetch(fa, 0, ch_a != ch_b);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        compute(fb, 1, u_b);
+        HXQ_LEAN_COMMIT();
+        if (alive) compute(fb, 1, u_b);
+#if HXQ_GEMV_TMA
+        phase ^= 1u;
+#endif
     }
+#if HXQ_GEMV_TMA
+    if (!alive) {   // let the copy that never reported finish before the CTA's memory goes away
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000000LL) { }
+    }
+#else
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+#endif
+#undef HXQ_LEAN_COMMIT
+#undef HXQ_LEAN_LANDED
     __syncthreads();
 
     // ---- add the chunks of each row block in chunk order; lane j owns value j = row * MP + token ----
@@ -974,9 +1052,6 @@ GemvPlan gemv_plan(const hxq_desc* d, int MP, int n_sm) {
         if (w % p.nch != 0) score *= 0.97;
         if (score > best + 1e-9) { best = score; p.warps_per_cta = w; }
     }
-#ifdef HXQ_GEMV_WFORCE
-    if (MP == 1) p.warps_per_cta = HXQ_GEMV_WFORCE;
-#endif
     p.counter_bytes = (((size_t)p.nrb * sizeof(unsigned int)) + 255) & ~(size_t)255;
     p.scratch_bytes = (p.nch > 1) ? (size_t)p.nrb * p.max_parts * RM * sizeof(float) : 0;
     return p;
@@ -986,7 +1061,7 @@ GemvPlan gemv_plan(const hxq_desc* d, int MP, int n_sm) {
 // index bytes per warp fit beside the table.
 static int lean_slot_bytes(const GemvPlan& p, int MP) {
     const int64_t slots = (p.units + p.grid - 1) / p.grid + p.nch - 1;
-    const int64_t b = (slots * kRows * MP * 4 + 127) & ~127LL;
+    const int64_t b = ((slots * kRows * MP * 4 + 127) & ~127LL) + kLeanBarBytes;
     return b > (1 << 20) ? (1 << 20) : (int)b;
 }
 // Most warps whose staging (two 4 KB unit buffers + one chunk of activations each) fits beside the
@@ -996,6 +1071,40 @@ static int lean_max_warps(const GemvPlan& p, int MP, int x_dtype) {
     const int64_t room = (int64_t)kLeanSmemBytes - kLutBytes - lean_slot_bytes(p, MP) - 256 - kRows * kChunk;
     return room > 0 ? (int)(room / per_warp) : 0;
 }
+// The index matrix as a 2-D tensor of 32-bit words for the bulk tensor copies (a box is at most
+// 256 elements wide: 128 words are the 512 index bytes of one chunk), 8 rows per box.  The
+// encoder is a driver entry point, looked up once.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn gemv_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* q = nullptr;
+        cudaDriverEntryPointQueryResult r;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &q, cudaEnableDefault, &r) == cudaSuccess &&
+            r == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(q);
+    }
+    return fn;
+}
+static bool gemv_index_map(CUtensorMap* map, const hxq_desc* d) {
+#if HXQ_GEMV_TMA
+    EncodeTiledFn fn = gemv_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)(d->in_features / 4), (cuuint64_t)d->out_features};
+    const cuuint64_t strides[1] = {(cuuint64_t)d->ld_idx};
+    const cuuint32_t box[2] = {kChunk / 4, kRows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(d->indices), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+#else
+    memset(map, 0, sizeof(*map));
+    return true;
+#endif
+}
+
 static bool gemv_lean_shape(const hxq_desc* d, const GemvPlan& p, bool x_vec) {
 #ifdef HXQ_GEMV_NO_LEAN
     return false;
@@ -1007,7 +1116,8 @@ static bool gemv_lean_shape(const hxq_desc* d, const GemvPlan& p, bool x_vec) {
 }
 
 template <int MP>
-static int launch_fast(const GemvArgs& a, const GemvPlan& p, bool lean, cudaStream_t stream) {
+static int launch_fast(const GemvArgs& a, const GemvPlan& p, const CUtensorMap* tmap, cudaStream_t stream) {
+    const bool lean = tmap != nullptr;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1028,7 +1138,7 @@ static int launch_fast(const GemvArgs& a, const GemvPlan& p, bool lean, cudaStre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = lean ? cudaLaunchKernelEx(&cfg, gemv_lean_kernel<MP>, a) : cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a);
+    const cudaError_t e = lean ? cudaLaunchKernelEx(&cfg, gemv_lean_kernel<MP>, *tmap, a) : cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a);
     return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
@@ -1079,11 +1189,13 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
             if (pl.warps_per_cta > wfit) pl.warps_per_cta = wfit;
             lean = pl.warps_per_cta >= 4;
         }
+        CUtensorMap tmap;
+        if (lean) lean = gemv_index_map(&tmap, d);
         a.slot_bytes = lean ? lean_slot_bytes(p, MP) : 0;
         int st;
-        if (MP == 1) st = launch_fast<1>(a, lean ? pl : p, lean, stream);
-        else if (MP == 2) st = launch_fast<2>(a, lean ? pl : p, lean, stream);
-        else st = launch_fast<4>(a, lean ? pl : p, lean, stream);
+        if (MP == 1) st = launch_fast<1>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
+        else if (MP == 2) st = launch_fast<2>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
+        else st = launch_fast<4>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
         if (st != HXQ_OK) return st;
         m0 += mm;
     }
