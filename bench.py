@@ -424,7 +424,10 @@ def main():
                        + ("python launches" if graph is None else "step captured in a CUDA graph") + ", host sync per step"},
         "gpu_launches": n_launch_per_step * K,
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                     "peak_kind": f"of {peak_kind}", "frac_of_8TBps": per_gpu / 8000.0, "traffic": None,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8TBps": per_gpu / 8000.0,
+                     # dram__bytes_read + dram__bytes_write per launch from the ncu capture summarised in
+                     # profiles/gemv_kernel_m1_qwen7b_mlp.md (gate 73.64 MB, down 73.90 MB; M = 1, one GPU)
+                     "traffic": (2 * 73.64e6 + 73.90e6) / 3 if (M == 1 and world == 1 and L > 0) else None,
                      "kernel": "hxq::gemv_lean_kernel<1>" if M == 1 else "hxq::gemv_lean_kernel",
                      "algorithmic_bytes_per_launch": nbytes_rank / (3 * L),
                      "avg_launch_us": ms_step * 1e3 / (3 * L)},
