@@ -74,6 +74,22 @@ def lib() -> C.CDLL:
                            C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     L.hxq_csr_from_positions.restype = C.c_int
     L.hxq_csr_from_positions.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+    L.hxq_add_rmsnorm.restype = C.c_int
+    L.hxq_add_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                  C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_void_p]
+    L.hxq_rope_append.restype = C.c_int
+    L.hxq_rope_append.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                  C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_void_p]
+    L.hxq_attn_decode_workspace_bytes.restype = C.c_size_t
+    L.hxq_attn_decode_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+    L.hxq_attn_decode.restype = C.c_int
+    L.hxq_attn_decode.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                  C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_float, C.c_void_p]
+    L.hxq_swiglu.restype = C.c_int
+    L.hxq_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
+                             C.c_int64, C.c_void_p]
     _lib = L
     return L
 

@@ -1,0 +1,305 @@
+// hxq_decode: the small kernels between the compressed linears of one decode step
+// (one new token per sequence): residual add + RMSNorm, rotary embedding + KV-cache
+// append, single-query grouped attention over the cache, SwiGLU.  The reference runs
+// these as dozens of framework element-wise launches per layer around its linears
+// (helix_substrate/basin_runtime.py:358-445 drives a stock HF Qwen2 forward per token);
+// here each is one launch, bf16 in / bf16 out with fp32 arithmetic inside, rounded at
+// the same places as the framework ops they replace.
+//
+// All kernels read the decode position from device memory, so a captured CUDA graph of
+// the step can be replayed for every token.
+
+#include <cuda_bf16.h>
+
+#include "hxq_common.cuh"
+
+namespace hxq {
+namespace dec {
+
+__device__ __forceinline__ float bf(const __nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ __nv_bfloat16 to_bf(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {   // blockDim.x <= 1024, all threads call
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    __syncthreads();
+    return t;
+}
+
+// h[b,:] += delta[b,:] (bf16 add, skipped when delta == nullptr); out[b,:] = bf16(bf16(h * rsqrt(mean(h^2) + eps)) * w).
+// One CTA per row, 8 elements per thread per step.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                                                          const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                                          int H, int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps) {
+    __shared__ float red[32];
+    extern __shared__ float row[];   // the updated row in fp32
+    __nv_bfloat16* hp = h + (int64_t)blockIdx.x * ld_h;
+    const __nv_bfloat16* dp = delta ? delta + (int64_t)blockIdx.x * ld_delta : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = bf(hp[i]);
+        if (dp) {
+            v = bf(to_bf(v + bf(dp[i])));
+            hp[i] = to_bf(v);
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    const float tot = block_sum(ss, red);
+    const float rs = rsqrtf(tot / (float)H + eps);
+    __nv_bfloat16* op = out + (int64_t)blockIdx.x * ld_out;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) op[i] = to_bf(bf(to_bf(row[i] * rs)) * bf(w[i]));
+}
+
+// Rotary embedding (rotate-half convention) of the new token's q and k heads, k and v appended to the
+// cache at row `pos`.  Grid (nq + 2 nkv, B), D/2 threads: thread i owns the pair (i, i + D/2).
+__global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld_qkv, const int64_t* __restrict__ pos_p,
+                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                   __nv_bfloat16* __restrict__ q_out, int64_t ld_q,
+                                   __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                   int nq, int nkv, int D, int max_len) {
+    const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = D >> 1;
+    const int64_t pos = *pos_p;
+    if (pos < 0 || pos >= max_len) return;
+    const __nv_bfloat16* src = qkv + (int64_t)b * ld_qkv + (int64_t)head * D;
+    if (head >= nq + nkv) {   // v: plain copy
+        __nv_bfloat16* dst = v_cache + (((int64_t)b * nkv + (head - nq - nkv)) * max_len + pos) * D;
+        dst[i] = src[i];
+        dst[i + half] = src[i + half];
+        return;
+    }
+    const float c0 = cos_t[pos * D + i], s0 = sin_t[pos * D + i];
+    const float c1 = cos_t[pos * D + i + half], s1 = sin_t[pos * D + i + half];
+    const float x0 = bf(src[i]), x1 = bf(src[i + half]);
+    // x * cos + rotate_half(x) * sin, with rotate_half(x) = [-x1, x0], each product rounded as the framework's fp32 ops are
+    const __nv_bfloat16 o0 = to_bf(x0 * c0 + (-x1) * s0);
+    const __nv_bfloat16 o1 = to_bf(x1 * c1 + x0 * s1);
+    __nv_bfloat16* dst = (head < nq) ? q_out + (int64_t)b * ld_q + (int64_t)head * D
+                                     : k_cache + (((int64_t)b * nkv + (head - nq)) * max_len + pos) * D;
+    dst[i] = o0;
+    dst[i + half] = o1;
+}
+
+constexpr int kAttnChunk = 64;     // cache positions per CTA
+constexpr int kAttnThreads = 128;
+constexpr int kAttnMaxGroup = 8;   // query heads per KV head
+constexpr int kAttnMaxD = 128;
+
+// One CTA: positions [c*64, c*64+64) of one (sequence, KV head), all query heads of the group.
+// Writes per (b, query head, chunk): running max m, sum l and the un-normalised output o[D] (fp32).
+__global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_bfloat16* __restrict__ q, int64_t ld_q,
+                                                                    const __nv_bfloat16* __restrict__ k_cache,
+                                                                    const __nv_bfloat16* __restrict__ v_cache,
+                                                                    const int64_t* __restrict__ pos_p, float* __restrict__ part,
+                                                                    int nq, int nkv, int D, int max_len, int n_chunks, float scale) {
+    const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
+    const int64_t pos = *pos_p;
+    const int p0 = c * kAttnChunk;
+    if (p0 > pos || pos >= max_len) return;
+    const int G = nq / nkv;
+    const int n_valid = (int)((pos - p0 + 1 < kAttnChunk) ? pos - p0 + 1 : kAttnChunk);
+
+    __shared__ __align__(16) float q_s[kAttnMaxGroup][kAttnMaxD];
+    __shared__ __align__(16) __nv_bfloat16 kv_s[kAttnChunk][kAttnMaxD + 8];   // +16 B per row: rows start in different banks
+    __shared__ float s_s[kAttnMaxGroup][kAttnChunk];
+    __shared__ float m_s[kAttnMaxGroup], l_s[kAttnMaxGroup];
+
+    for (int i = t; i < G * D; i += kAttnThreads) {
+        const int g = i / D, d = i - g * D;
+        q_s[g][d] = bf(q[(int64_t)b * ld_q + (int64_t)(kvh * G + g) * D + d]) * scale;
+    }
+    const int64_t base = (((int64_t)b * nkv + kvh) * max_len + p0) * D;
+    const int vec_per_row = D / 8;    // 16-byte pieces per row
+    for (int i = t; i < n_valid * vec_per_row; i += kAttnThreads) {
+        const int r = i / vec_per_row, v = i - r * vec_per_row;
+        *reinterpret_cast<uint4*>(&kv_s[r][v * 8]) = *reinterpret_cast<const uint4*>(k_cache + base + (int64_t)r * D + v * 8);
+    }
+    __syncthreads();
+
+    // scores: thread (p = t % 64, hg = t / 64) takes query heads hg, hg + 2, ... of position p
+    {
+        const int p = t & (kAttnChunk - 1), hg = t / kAttnChunk;
+        float acc[kAttnMaxGroup / 2];
+#pragma unroll
+        for (int j = 0; j < kAttnMaxGroup / 2; ++j) acc[j] = 0.f;
+        if (p < n_valid) {
+            for (int d = 0; d < D; d += 8) {
+                const uint4 kk = *reinterpret_cast<const uint4*>(&kv_s[p][d]);
+                const uint32_t w[4] = {kk.x, kk.y, kk.z, kk.w};
+                float kf[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    kf[2 * e] = __uint_as_float(w[e] << 16);
+                    kf[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                }
+#pragma unroll
+                for (int j = 0; j < kAttnMaxGroup / 2; ++j) {
+                    const int g = hg + 2 * j;
+                    if (g < G) {
+                        const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][d]);
+                        const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][d + 4]);
+                        acc[j] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w
+                                + kf[4] * qb.x + kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kAttnMaxGroup / 2; ++j) {
+            const int g = hg + 2 * j;
+            if (g < G) s_s[g][p] = (p < n_valid) ? acc[j] : -INFINITY;
+        }
+    }
+    __syncthreads();
+
+    // V over K's buffer (everyone is done with K), softmax pieces per head meanwhile
+    for (int i = t; i < n_valid * vec_per_row; i += kAttnThreads) {
+        const int r = i / vec_per_row, v = i - r * vec_per_row;
+        *reinterpret_cast<uint4*>(&kv_s[r][v * 8]) = *reinterpret_cast<const uint4*>(v_cache + base + (int64_t)r * D + v * 8);
+    }
+    {
+        const int warp = t >> 5, lane = t & 31;
+        for (int g = warp; g < G; g += kAttnThreads / 32) {
+            const float a0 = s_s[g][lane], a1 = s_s[g][lane + 32];
+            float m = fmaxf(a0, a1);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const float e0 = __expf(a0 - m), e1 = __expf(a1 - m);   // exp(-inf) = 0 for the masked tail
+            float l = e0 + e1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            s_s[g][lane] = e0;
+            s_s[g][lane + 32] = e1;
+            if (lane == 0) { m_s[g] = m; l_s[g] = l; }
+        }
+    }
+    __syncthreads();
+
+    // o[g][d] = sum_p prob[g][p] * V[p][d]; thread t owns dimension d = t (and d + 128 ... if D > 128: not supported)
+    if (t < D) {
+        float o[kAttnMaxGroup];
+#pragma unroll
+        for (int g = 0; g < kAttnMaxGroup; ++g) o[g] = 0.f;
+        for (int p = 0; p < n_valid; ++p) {
+            const float v = bf(kv_s[p][t]);
+#pragma unroll
+            for (int g = 0; g < kAttnMaxGroup; ++g)
+                if (g < G) o[g] += s_s[g][p] * v;
+        }
+#pragma unroll
+        for (int g = 0; g < kAttnMaxGroup; ++g)
+            if (g < G) {
+                float* dst = part + (((int64_t)b * nq + kvh * G + g) * n_chunks + c) * (D + 2);
+                dst[2 + t] = o[g];
+                if (t == 0) { dst[0] = m_s[g]; dst[1] = l_s[g]; }
+            }
+    }
+}
+
+// out[b, head, :] = sum_c exp(m_c - M) o_c / sum_c exp(m_c - M) l_c over the chunks up to the position.
+__global__ void __launch_bounds__(kAttnMaxD) attn_combine_kernel(const float* __restrict__ part, const int64_t* __restrict__ pos_p,
+                                                                __nv_bfloat16* __restrict__ out, int64_t ld_out,
+                                                                int nq, int D, int max_len, int n_chunks) {
+    const int head = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    const int64_t pos = *pos_p;
+    if (pos < 0 || pos >= max_len || t >= D) return;
+    const int nc = (int)(pos / kAttnChunk) + 1;
+    const float* src = part + ((int64_t)b * nq + head) * n_chunks * (D + 2);
+    float M = -INFINITY;
+    for (int c = 0; c < nc; ++c) M = fmaxf(M, src[c * (D + 2)]);
+    float L = 0.f, o = 0.f;
+    for (int c = 0; c < nc; ++c) {
+        const float w = __expf(src[c * (D + 2)] - M);
+        L += w * src[c * (D + 2) + 1];
+        o += w * src[c * (D + 2) + 2 + t];
+    }
+    out[(int64_t)b * ld_out + (int64_t)head * D + t] = to_bf(o / L);
+}
+
+// out = bf16(bf16(silu(gate)) * up), element-wise over [B, n].
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                              __nv_bfloat16* __restrict__ out, int n, int64_t ld_g, int64_t ld_u, int64_t ld_o) {
+    const int b = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    const __nv_bfloat16* g = gate + (int64_t)b * ld_g;
+    const __nv_bfloat16* u = up + (int64_t)b * ld_u;
+    __nv_bfloat16* o = out + (int64_t)b * ld_o;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        if (i + k < n) {
+            const float x = bf(g[i + k]);
+            const float s = bf(to_bf(x / (1.f + __expf(-x))));
+            o[i + k] = to_bf(s * bf(u[i + k]));
+        }
+    }
+}
+
+}  // namespace dec
+}  // namespace hxq
+
+using namespace hxq::dec;
+
+extern "C" int hxq_add_rmsnorm(void* h, const void* delta, const void* weight, void* out, int32_t B, int32_t H,
+                               int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps, hxq_stream_t stream) {
+    if (!h || !weight || !out || B <= 0 || H <= 0) return HXQ_E_ARG;
+    if (H > 12000) return HXQ_E_SHAPE;   // the row is kept in shared memory
+    add_rmsnorm_kernel<<<B, 256, H * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<__nv_bfloat16*>(h), reinterpret_cast<const __nv_bfloat16*>(delta),
+        reinterpret_cast<const __nv_bfloat16*>(weight), reinterpret_cast<__nv_bfloat16*>(out), H, ld_h, ld_delta, ld_out, eps);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+extern "C" int hxq_rope_append(const void* qkv, int64_t ld_qkv, const int64_t* pos, const float* cos_table,
+                               const float* sin_table, void* q_out, int64_t ld_q, void* k_cache, void* v_cache,
+                               int32_t B, int32_t nq, int32_t nkv, int32_t D, int32_t max_len, hxq_stream_t stream) {
+    if (!qkv || !pos || !cos_table || !sin_table || !q_out || !k_cache || !v_cache) return HXQ_E_ARG;
+    if (B <= 0 || nq <= 0 || nkv <= 0 || D <= 0 || (D & 1) || D > 2048 || max_len <= 0) return HXQ_E_SHAPE;
+    rope_append_kernel<<<dim3(nq + 2 * nkv, B), D / 2, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(qkv), ld_qkv, pos, cos_table, sin_table,
+        reinterpret_cast<__nv_bfloat16*>(q_out), ld_q, reinterpret_cast<__nv_bfloat16*>(k_cache),
+        reinterpret_cast<__nv_bfloat16*>(v_cache), nq, nkv, D, max_len);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+extern "C" size_t hxq_attn_decode_workspace_bytes(int32_t B, int32_t nq, int32_t D, int32_t max_len) {
+    if (B <= 0 || nq <= 0 || D <= 0 || max_len <= 0) return 0;
+    const size_t n_chunks = ((size_t)max_len + kAttnChunk - 1) / kAttnChunk;
+    return (size_t)B * nq * n_chunks * (D + 2) * sizeof(float);
+}
+
+extern "C" int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache, const void* v_cache, const int64_t* pos,
+                               void* out, int64_t ld_out, void* workspace, size_t workspace_bytes, int32_t B, int32_t nq,
+                               int32_t nkv, int32_t D, int32_t max_len, float scale, hxq_stream_t stream) {
+    if (!q || !k_cache || !v_cache || !pos || !out) return HXQ_E_ARG;
+    if (B <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > kAttnMaxGroup) return HXQ_E_SHAPE;
+    if (D <= 0 || D > kAttnMaxD || D % 8 != 0 || max_len <= 0) return HXQ_E_SHAPE;
+    if (!hxq::aligned_to(k_cache, 16) || !hxq::aligned_to(v_cache, 16)) return HXQ_E_ALIGN;
+    if (!workspace || workspace_bytes < hxq_attn_decode_workspace_bytes(B, nq, D, max_len)) return HXQ_E_WORKSPACE;
+    const int n_chunks = (max_len + kAttnChunk - 1) / kAttnChunk;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    attn_partial_kernel<<<dim3(n_chunks, nkv, B), kAttnThreads, 0, s>>>(
+        reinterpret_cast<const __nv_bfloat16*>(q), ld_q, reinterpret_cast<const __nv_bfloat16*>(k_cache),
+        reinterpret_cast<const __nv_bfloat16*>(v_cache), pos, reinterpret_cast<float*>(workspace), nq, nkv, D, max_len,
+        n_chunks, scale);
+    if (cudaGetLastError() != cudaSuccess) return HXQ_E_LAUNCH;
+    attn_combine_kernel<<<dim3(nq, B), kAttnMaxD, 0, s>>>(reinterpret_cast<const float*>(workspace), pos,
+                                                          reinterpret_cast<__nv_bfloat16*>(out), ld_out, nq, D, max_len, n_chunks);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+extern "C" int hxq_swiglu(const void* gate, const void* up, void* out, int32_t B, int32_t n, int64_t ld_gate,
+                          int64_t ld_up, int64_t ld_out, hxq_stream_t stream) {
+    if (!gate || !up || !out || B <= 0 || n <= 0) return HXQ_E_ARG;
+    const int threads = 256, per_block = threads * 2;
+    swiglu_kernel<<<dim3((n + per_block - 1) / per_block, B), threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(gate), reinterpret_cast<const __nv_bfloat16*>(up),
+        reinterpret_cast<__nv_bfloat16*>(out), n, ld_gate, ld_up, ld_out);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}

@@ -566,8 +566,11 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
         ring_q0 = (i0 < n_lo ? lo0 + i0 * kUnitBytes : hi0 + (i0 - n_lo) * kUnitBytes) + lane * 16;
         ring_q1 = (i1 < n_lo ? lo0 + i1 * kUnitBytes : hi0 + (i1 - n_lo) * kUnitBytes) + lane * 16;
         const uint32_t n_hi = n_q > n_lo ? n_q - n_lo : 0u;
-        ring_x = hi0 + n_hi * kUnitBytes + warp * (MP * 32 * xs_lane) + lane * xs_lane;   // token m at + m * 32 * xs_lane
+        // token m at + m * 32 * xs_lane; a lane's 16-byte pieces 512 bytes apart (conflict-free) unless
+        // a bulk copy lays the chunk down contiguously
+        ring_x = hi0 + n_hi * kUnitBytes + warp * (MP * 32 * xs_lane) + lane * (HXQ_GEMV_TMA ? xs_lane : 16);
     }
+    constexpr int kXPiece = HXQ_GEMV_TMA ? 16 : 512;   // distance between a lane's consecutive 16-byte pieces
 #if HXQ_GEMV_TMA
     // one mbarrier per unit buffer, at the end of the slot area; only this warp ever touches its two
     const uint32_t bar0 = lut_base + kLutBytes + (uint32_t)a.slot_bytes - kLeanBarBytes + warp * 16;
@@ -638,10 +641,10 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
                 if (m < a.M) {
                     const char* xm = xg + (size_t)m * a.ldx * (xs_lane >> 4);
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane), "l"(xm) : "memory");
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 16), "l"(xm + 16) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + kXPiece), "l"(xm + 16) : "memory");
                     if (xs_lane == 64) {
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 32), "l"(xm + 32) : "memory");
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 48), "l"(xm + 48) : "memory");
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 2 * kXPiece), "l"(xm + 32) : "memory");
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + 3 * kXPiece), "l"(xm + 48) : "memory");
                     }
                 }
             }
@@ -715,7 +718,7 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
                 if (k < nq)
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                  : "=r"(w[4 * k]), "=r"(w[4 * k + 1]), "=r"(w[4 * k + 2]), "=r"(w[4 * k + 3])
-                                 : "r"(ring_x + m * 32 * xs_lane + 16 * k));
+                                 : "r"(ring_x + m * 32 * xs_lane + kXPiece * k));
             }
             if (a.x_dtype == HXQ_F32) {
 #pragma unroll

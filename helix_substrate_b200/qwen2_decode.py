@@ -2,10 +2,11 @@
 
 This is the caller around the compressed-linear path (the reference drives HF
 models with a Python greedy loop, helix_substrate/basin_runtime.py:358-445, at
-one model() call per token): RMSNorm, RoPE, grouped-query attention over a
-static KV cache and SwiGLU in plain torch ops, every projection an HXQ product,
-and the whole one-token step replayed from a CUDA graph so that the ~200 kernel
-launches per token cost no Python time.  Tensor parallel: q/k/v/gate/up are
+one model() call per token): every projection is an HXQ product; the one-token
+step runs RMSNorm (+ residual add), RoPE + KV-cache append, single-query
+grouped attention and SwiGLU as one launch each (decode_ops: 13 launches per
+layer) and is replayed from a CUDA graph; the prompt is prefilled with the same
+operators written in plain torch ops (also the parity reference of the step).  Tensor parallel: q/k/v/gate/up are
 column-parallel, o/down row-parallel with one all-reduce each (NCCL).
 
 Weights are random-init (N(0, 0.02)) and compressed on the GPU; lm_head and the
@@ -21,6 +22,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import decode_ops
 from .helix_linear import HelixLinear
 from .hxq_writer_gpu import compress_weight
 from .tp import shard_helix_linear
@@ -153,6 +155,47 @@ class Qwen2HxqDecoder(nn.Module):
         h = self._rms(h[:, -1], self.norm)
         return h @ self.lm_head.t()
 
+    def _step_buffers(self, B: int):
+        sb = getattr(self, "_sb", None)
+        if sb is None or sb["h"].shape[0] != B:
+            L0, D, dev = self.layers[0], self.shp.head_dim, self.device
+            mk = lambda n: torch.empty(B, n, device=dev, dtype=torch.bfloat16)
+            sb = dict(h=mk(self.shp.hidden), x=mk(self.shp.hidden), qkv=mk((L0.n_q + 2 * L0.n_kv) * D),
+                      q=mk(L0.n_q * D), a=mk(L0.n_q * D), g=mk(L0.gate_proj.out_features),
+                      u=mk(L0.gate_proj.out_features), act=mk(L0.gate_proj.out_features),
+                      d1=mk(self.shp.hidden), d2=mk(self.shp.hidden))
+            self._sb = sb
+        return sb
+
+    def step_fused(self, tok: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """One decode step for tok [B, 1] at position pos (int64 device tensor [1]): same
+        arithmetic as ``forward_tokens(tok, pos, pos, None)`` with the glue between the
+        linears in four fused operators.  Returns the logits [B, vocab]."""
+        B = tok.shape[0]
+        sb = self._step_buffers(B)
+        D, eps = self.shp.head_dim, self.shp.rms_eps
+        bf = torch.bfloat16
+        h, x = sb["h"], sb["x"]
+        h.copy_(self.embed[tok[:, 0]])
+        delta = None
+        for li, L in enumerate(self.layers):
+            nq, nkv = L.n_q, L.n_kv
+            decode_ops.add_rmsnorm(h, delta, L.ln1, eps, x)
+            qkv = sb["qkv"]
+            L.q_proj.packed().matmul(x, bf, out=qkv[:, : nq * D])
+            L.k_proj.packed().matmul(x, bf, out=qkv[:, nq * D: (nq + nkv) * D])
+            L.v_proj.packed().matmul(x, bf, out=qkv[:, (nq + nkv) * D:])
+            decode_ops.rope_append(qkv, pos, self.cos, self.sin, sb["q"], self.k_cache[li], self.v_cache[li], nq, nkv)
+            decode_ops.attn_decode(sb["q"], self.k_cache[li], self.v_cache[li], pos, sb["a"], nq, D ** -0.5)
+            delta = self._allreduce(L.o_proj.packed().matmul(sb["a"], bf, out=sb["d1"]))
+            decode_ops.add_rmsnorm(h, delta, L.ln2, eps, x)
+            L.gate_proj.packed().matmul(x, bf, out=sb["g"])
+            L.up_proj.packed().matmul(x, bf, out=sb["u"])
+            decode_ops.swiglu(sb["g"], sb["u"], sb["act"])
+            delta = self._allreduce(L.down_proj.packed().matmul(sb["act"], bf, out=sb["d2"]))
+        decode_ops.add_rmsnorm(h, delta, self.norm, eps, x)
+        return x @ self.lm_head.t()
+
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
         T = prompt.shape[1]
@@ -164,7 +207,7 @@ class Qwen2HxqDecoder(nn.Module):
         return logits.argmax(-1)
 
     @torch.no_grad()
-    def make_graphed_step(self, batch: int):
+    def make_graphed_step(self, batch: int, fused: bool = True):
         """Capture the one-token step.  Returns (run, tok, pos): write the
         current tokens into ``tok`` [B, 1] and the position into ``pos`` [1],
         call ``run()``, read the next tokens from its result."""
@@ -172,6 +215,8 @@ class Qwen2HxqDecoder(nn.Module):
         pos = torch.zeros(1, device=self.device, dtype=torch.long)
 
         def body():
+            if fused:
+                return self.step_fused(tok, pos).argmax(-1)
             return self.forward_tokens(tok, pos, pos, None).argmax(-1)
 
         side = torch.cuda.Stream()
@@ -226,6 +271,7 @@ def main(argv=None):
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--torch-glue", action="store_true", help="run the step's glue in plain torch ops")
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -251,7 +297,7 @@ def main(argv=None):
         if args.no_graph:
             run = None
         else:
-            run, tok, pos = model.make_graphed_step(args.batch)
+            run, tok, pos = model.make_graphed_step(args.batch, fused=not args.torch_glue)
         torch.cuda.synchronize()
         # timed decode: new-1 graph replays
         e1.record()
@@ -278,6 +324,7 @@ def main(argv=None):
             "metric": "decode_tokens_per_s", "value": args.batch * 1000.0 / ms_dec, "unit": "tok/s",
             "ms_per_token_step": ms_dec, "batch": args.batch, "prompt": args.prompt, "new_tokens": args.new,
             "shape": args.shape, "layers": shp.layers, "n_gpus": world, "launch": "python" if run is None else "cuda_graph",
+            "glue": "torch" if (args.torch_glue or run is None) else "fused",
             "hxq_algorithmic_bytes_per_step_per_gpu": hxq_bytes,
             "hxq_GBps_per_gpu_if_all_time_were_linears": hxq_bytes / (ms_dec * 1e-3) / 1e9,
             "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,

@@ -159,6 +159,43 @@ int hxq_gemm(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t l
              hxq_stream_t stream);
 
 /*
+ * ---- decode-step glue (bf16): the small operators between the compressed linears ----
+ * The reference decodes with a stock HF Qwen2 forward per token
+ * (helix_substrate/basin_runtime.py:358-445: model(...) inside a Python greedy loop), i.e.
+ * dozens of framework element-wise launches per layer around the linears.  These four
+ * entry points are those operators as one launch each, so that a decode step is
+ * 13 launches per layer.  All tensors bf16 unless noted, strides in elements, the
+ * decode position read from DEVICE memory (int64) so a captured step can be replayed.
+ */
+
+/* h[b,:] += delta[b,:] (skipped if delta is NULL), then out[b,:] = rmsnorm(h[b,:]) * weight,
+ * fp32 statistics, rounded to bf16 before and after the weight product like
+ * Qwen2RMSNorm (reference models: transformers' modeling_qwen2, driven by
+ * helix_substrate/basin_runtime.py:281-330).  H <= 12000. */
+int hxq_add_rmsnorm(void* h, const void* delta, const void* weight, void* out, int32_t B, int32_t H,
+                    int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps, hxq_stream_t stream);
+
+/* qkv[b, :] holds the new token's nq query heads, then nkv key heads, then nkv value heads
+ * (D each).  Applies the rotary embedding (rotate-half convention, cos/sin fp32 tables
+ * [max_len, D]) to q and k at row *pos, writes q to q_out[b, nq*D] and appends k, v to the
+ * caches [B, nkv, max_len, D] at row *pos. */
+int hxq_rope_append(const void* qkv, int64_t ld_qkv, const int64_t* pos, const float* cos_table,
+                    const float* sin_table, void* q_out, int64_t ld_q, void* k_cache, void* v_cache,
+                    int32_t B, int32_t nq, int32_t nkv, int32_t D, int32_t max_len, hxq_stream_t stream);
+
+/* Single-query grouped attention over cache rows 0..*pos: out[b, h*D + d] =
+ * softmax_p(scale * q[b,h,:] . K[b, h / (nq/nkv), p, :]) V[...].  D <= 128, D % 8 == 0,
+ * nq / nkv <= 8.  workspace: hxq_attn_decode_workspace_bytes() of plain scratch. */
+size_t hxq_attn_decode_workspace_bytes(int32_t B, int32_t nq, int32_t D, int32_t max_len);
+int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache, const void* v_cache, const int64_t* pos,
+                    void* out, int64_t ld_out, void* workspace, size_t workspace_bytes, int32_t B, int32_t nq,
+                    int32_t nkv, int32_t D, int32_t max_len, float scale, hxq_stream_t stream);
+
+/* out[b, i] = silu(gate[b, i]) * up[b, i], i < n (the MLP between gate/up and down). */
+int hxq_swiglu(const void* gate, const void* up, void* out, int32_t B, int32_t n, int64_t ld_gate,
+               int64_t ld_up, int64_t ld_out, hxq_stream_t stream);
+
+/*
  * Host helper: CSR row pointer from ascending flat positions
  * (rows = pos / in_features), the derivation HelixLinear does at load
  * (helix_substrate/helix_linear.py:196-203,960-997).  positions, rowptr and
