@@ -7,9 +7,14 @@
 // the same places as the framework ops they replace.
 //
 // All kernels read the decode position from device memory, so a captured CUDA graph of
-// the step can be replayed for every token.
+// the step can be replayed for every token.  They are launched with programmatic stream
+// serialisation and open with griddepcontrol.launch_dependents / griddepcontrol.wait: the
+// launch itself overlaps the tail of whatever precedes them in the stream (the compressed
+// linears do the same), and nothing is read before the predecessor has completed.
 
 #include <cuda_bf16.h>
+
+#include <utility>
 
 #include "hxq_common.cuh"
 
@@ -18,6 +23,27 @@ namespace dec {
 
 __device__ __forceinline__ float bf(const __nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ __nv_bfloat16 to_bf(float v) { return __float2bfloat16_rn(v); }
+
+// Let the next kernel in the stream be scheduled, then wait until everything before this one is done.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 __device__ __forceinline__ float block_sum(float v, float* red) {   // blockDim.x <= 1024, all threads call
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -39,6 +65,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restr
                                                           int H, int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps) {
     __shared__ float red[32];
     extern __shared__ float row[];   // the updated row in fp32
+    pdl_enter();
     __nv_bfloat16* hp = h + (int64_t)blockIdx.x * ld_h;
     const __nv_bfloat16* dp = delta ? delta + (int64_t)blockIdx.x * ld_delta : nullptr;
     float ss = 0.f;
@@ -65,6 +92,7 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, int64_
                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                    int nq, int nkv, int D, int max_len) {
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = D >> 1;
+    pdl_enter();
     const int64_t pos = *pos_p;
     if (pos < 0 || pos >= max_len) return;
     const __nv_bfloat16* src = qkv + (int64_t)b * ld_qkv + (int64_t)head * D;
@@ -99,6 +127,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
                                                                     const int64_t* __restrict__ pos_p, float* __restrict__ part,
                                                                     int nq, int nkv, int D, int max_len, int n_chunks, float scale) {
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
+    pdl_enter();
     const int64_t pos = *pos_p;
     const int p0 = c * kAttnChunk;
     if (p0 > pos || pos >= max_len) return;
@@ -207,6 +236,7 @@ __global__ void __launch_bounds__(kAttnMaxD) attn_combine_kernel(const float* __
                                                                 __nv_bfloat16* __restrict__ out, int64_t ld_out,
                                                                 int nq, int D, int max_len, int n_chunks) {
     const int head = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    pdl_enter();
     const int64_t pos = *pos_p;
     if (pos < 0 || pos >= max_len || t >= D) return;
     const int nc = (int)(pos / kAttnChunk) + 1;
@@ -227,6 +257,7 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv
                               __nv_bfloat16* __restrict__ out, int n, int64_t ld_g, int64_t ld_u, int64_t ld_o) {
     const int b = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    pdl_enter();
     if (i >= n) return;
     const __nv_bfloat16* g = gate + (int64_t)b * ld_g;
     const __nv_bfloat16* u = up + (int64_t)b * ld_u;
@@ -250,10 +281,10 @@ extern "C" int hxq_add_rmsnorm(void* h, const void* delta, const void* weight, v
                                int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps, hxq_stream_t stream) {
     if (!h || !weight || !out || B <= 0 || H <= 0) return HXQ_E_ARG;
     if (H > 12000) return HXQ_E_SHAPE;   // the row is kept in shared memory
-    add_rmsnorm_kernel<<<B, 256, H * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(
+    const cudaError_t e = launch_pdl(add_rmsnorm_kernel, dim3(B), dim3(256), H * sizeof(float), reinterpret_cast<cudaStream_t>(stream),
         reinterpret_cast<__nv_bfloat16*>(h), reinterpret_cast<const __nv_bfloat16*>(delta),
-        reinterpret_cast<const __nv_bfloat16*>(weight), reinterpret_cast<__nv_bfloat16*>(out), H, ld_h, ld_delta, ld_out, eps);
-    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+        reinterpret_cast<const __nv_bfloat16*>(weight), reinterpret_cast<__nv_bfloat16*>(out), (int)H, ld_h, ld_delta, ld_out, eps);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
 extern "C" int hxq_rope_append(const void* qkv, int64_t ld_qkv, const int64_t* pos, const float* cos_table,
@@ -261,11 +292,11 @@ extern "C" int hxq_rope_append(const void* qkv, int64_t ld_qkv, const int64_t* p
                                int32_t B, int32_t nq, int32_t nkv, int32_t D, int32_t max_len, hxq_stream_t stream) {
     if (!qkv || !pos || !cos_table || !sin_table || !q_out || !k_cache || !v_cache) return HXQ_E_ARG;
     if (B <= 0 || nq <= 0 || nkv <= 0 || D <= 0 || (D & 1) || D > 2048 || max_len <= 0) return HXQ_E_SHAPE;
-    rope_append_kernel<<<dim3(nq + 2 * nkv, B), D / 2, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    const cudaError_t e = launch_pdl(rope_append_kernel, dim3(nq + 2 * nkv, B), dim3(D / 2), 0, reinterpret_cast<cudaStream_t>(stream),
         reinterpret_cast<const __nv_bfloat16*>(qkv), ld_qkv, pos, cos_table, sin_table,
         reinterpret_cast<__nv_bfloat16*>(q_out), ld_q, reinterpret_cast<__nv_bfloat16*>(k_cache),
-        reinterpret_cast<__nv_bfloat16*>(v_cache), nq, nkv, D, max_len);
-    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+        reinterpret_cast<__nv_bfloat16*>(v_cache), (int)nq, (int)nkv, (int)D, (int)max_len);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
 extern "C" size_t hxq_attn_decode_workspace_bytes(int32_t B, int32_t nq, int32_t D, int32_t max_len) {
@@ -284,22 +315,23 @@ extern "C" int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache,
     if (!workspace || workspace_bytes < hxq_attn_decode_workspace_bytes(B, nq, D, max_len)) return HXQ_E_WORKSPACE;
     const int n_chunks = (max_len + kAttnChunk - 1) / kAttnChunk;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    attn_partial_kernel<<<dim3(n_chunks, nkv, B), kAttnThreads, 0, s>>>(
-        reinterpret_cast<const __nv_bfloat16*>(q), ld_q, reinterpret_cast<const __nv_bfloat16*>(k_cache),
-        reinterpret_cast<const __nv_bfloat16*>(v_cache), pos, reinterpret_cast<float*>(workspace), nq, nkv, D, max_len,
-        n_chunks, scale);
-    if (cudaGetLastError() != cudaSuccess) return HXQ_E_LAUNCH;
-    attn_combine_kernel<<<dim3(nq, B), kAttnMaxD, 0, s>>>(reinterpret_cast<const float*>(workspace), pos,
-                                                          reinterpret_cast<__nv_bfloat16*>(out), ld_out, nq, D, max_len, n_chunks);
-    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+    if (launch_pdl(attn_partial_kernel, dim3(n_chunks, nkv, B), dim3(kAttnThreads), 0, s,
+                   reinterpret_cast<const __nv_bfloat16*>(q), ld_q, reinterpret_cast<const __nv_bfloat16*>(k_cache),
+                   reinterpret_cast<const __nv_bfloat16*>(v_cache), pos, reinterpret_cast<float*>(workspace), (int)nq, (int)nkv,
+                   (int)D, (int)max_len, n_chunks, scale) != cudaSuccess)
+        return HXQ_E_LAUNCH;
+    const cudaError_t e = launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(kAttnMaxD), 0, s,
+                                     reinterpret_cast<const float*>(workspace), pos, reinterpret_cast<__nv_bfloat16*>(out), ld_out,
+                                     (int)nq, (int)D, (int)max_len, n_chunks);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
 extern "C" int hxq_swiglu(const void* gate, const void* up, void* out, int32_t B, int32_t n, int64_t ld_gate,
                           int64_t ld_up, int64_t ld_out, hxq_stream_t stream) {
     if (!gate || !up || !out || B <= 0 || n <= 0) return HXQ_E_ARG;
     const int threads = 256, per_block = threads * 2;
-    swiglu_kernel<<<dim3((n + per_block - 1) / per_block, B), threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __nv_bfloat16*>(gate), reinterpret_cast<const __nv_bfloat16*>(up),
-        reinterpret_cast<__nv_bfloat16*>(out), n, ld_gate, ld_up, ld_out);
-    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+    const cudaError_t e = launch_pdl(swiglu_kernel, dim3((n + per_block - 1) / per_block, B), dim3(threads), 0,
+        reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(gate),
+        reinterpret_cast<const __nv_bfloat16*>(up), reinterpret_cast<__nv_bfloat16*>(out), (int)n, ld_gate, ld_up, ld_out);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }

@@ -1,6 +1,7 @@
 // hxq_gemm: prefill-time product on the tcgen05 tensor cores.
 //
-//   D[o, m] = sum_k W^[o, k] * x[m, k]      (o: 128 output rows per CTA, m: BN tokens)
+//   D[o, m] = sum_k W^[o, k] * x[m, k]      (o: 128 output rows per CTA, m: BN tokens; BN = 512 is two
+//                                            256-token accumulators fed by ONE dequantised weight tile)
 //
 // Only here is the path a dense contraction, so only here tensor cores are used.
 // One CTA owns a 128 x BN output tile; per 64-column K step
@@ -15,7 +16,10 @@
 //                      tcgen05.commit frees the stage
 //
 // and after the last step warps 2-5 read TMEM (tcgen05.ld), add the bias and store
-// y[m, o].  Three stages; every mbarrier wait is bounded and raises a status word.
+// y[m, o].  Three stages (two at BN = 512); every mbarrier wait is bounded and raises a status word.
+// The eight dequantising warps pace the kernel (about 800 issue cycles per K step against 525
+// tensor cycles for a 128x256x64 step), so the token tile is made as wide as TMEM allows: at
+// BN = 512 every dequantised tile feeds twice the tensor work.
 // No cluster launch and no multicast anywhere.
 
 #include <cuda.h>
@@ -33,7 +37,6 @@ namespace gemm {
 
 constexpr int BM = 128;        // output rows per CTA = UMMA M
 constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzled row
-constexpr int STAGES = 3;
 constexpr int LUT_BYTES = 256 * 128;   // entry c, lane l at byte c*128 + l*4
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int IDX_BYTES = BM * BK;     // 8 KB
@@ -41,6 +44,9 @@ constexpr int NUM_DEQ_WARPS = 8;
 constexpr int NUM_THREADS = 32 * (2 + NUM_DEQ_WARPS);
 
 template <int BN> struct Smem {
+    static constexpr int NSUB = BN > 256 ? 2 : 1;     // accumulators (UMMA N <= 256)
+    static constexpr int BNS = BN / NSUB;             // tokens per accumulator
+    static constexpr int STAGES = BN > 256 ? 2 : 3;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + IDX_BYTES;
     static constexpr int BAR_OFFSET = LUT_BYTES + STAGES * STAGE_BYTES;
@@ -72,6 +78,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x,
             const GemmArgs a) {
     using S = Smem<BN>;
+    constexpr int STAGES = S::STAGES;
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     char* lut = smem;
@@ -125,7 +132,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                 char* st = stage0 + s * S::STAGE_BYTES;
                 sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)(IDX_BYTES + S::B_BYTES));
                 sm100::tma_load_2d(st + A_BYTES + S::B_BYTES, &map_idx, &tma_full[s], ks * BK, o0);
-                sm100::tma_load_2d(st + A_BYTES, &map_x, &tma_full[s], ks * BK, m0);
+#pragma unroll
+                for (int n = 0; n < S::NSUB; ++n)
+                    sm100::tma_load_2d(st + A_BYTES + n * (S::BNS * BK * 2), &map_x, &tma_full[s], ks * BK, m0 + n * S::BNS);
                 armed = ks + 1;
             }
             if (*abort_flag != 0) {
@@ -137,7 +146,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = sm100::make_idesc_bf16(BM, BN);
+            constexpr uint32_t idesc = sm100::make_idesc_bf16(BM, S::BNS);
             bool ok = true;
             for (int ks = 0; ks < KS && ok; ++ks) {
                 const int s = ks % STAGES;
@@ -147,10 +156,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                 sm100::tc_fence_after_sync();
                 char* st = stage0 + s * S::STAGE_BYTES;
                 const uint64_t da = sm100::make_desc_k_sw128(sm100::smem_u32(st));
-                const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(st + A_BYTES));
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk)   // +32 bytes (>> 4 = 2) per 16-element K slice
-                    sm100::umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                for (int n = 0; n < S::NSUB; ++n) {    // accumulator n: TMEM columns [n * BNS, +BNS)
+                    const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(st + A_BYTES + n * (S::BNS * BK * 2)));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)   // +32 bytes (>> 4 = 2) per 16-element K slice
+                        sm100::umma_bf16(tmem_base + (uint32_t)(n * S::BNS), da + 2 * kk, db + 2 * kk, idesc,
+                                         (ks > 0 || kk > 0) ? 1u : 0u);
+                }
                 sm100::umma_commit(&empty[s]);
             }
             if (ok) sm100::umma_commit(acc_full);
@@ -379,13 +392,13 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
         xb = workspace;
         ldxb = ld;
     }
-    const int BN = M > 128 ? 256 : (M > 64 ? 128 : 64);
+    const int BN = M > 256 ? 512 : (M > 128 ? 256 : (M > 64 ? 128 : 64));
     CUtensorMap mi, mx;
     if (!make_map_2d(&mi, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->indices, (uint64_t)d->in_features,
                      (uint64_t)d->out_features, (uint64_t)d->ld_idx, BK, BM, CU_TENSOR_MAP_SWIZZLE_NONE))
         return HXQ_E_DEVICE;
     if (!make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, (uint64_t)d->in_features, (uint64_t)M,
-                     (uint64_t)ldxb * 2, BK, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B))
+                     (uint64_t)ldxb * 2, BK, (uint32_t)(BN > 256 ? 256 : BN), CU_TENSOR_MAP_SWIZZLE_128B))
         return HXQ_E_DEVICE;
     GemmArgs a;
     a.cb = d->codebook; a.scales = d->scales; a.offsets = d->offsets;
@@ -399,6 +412,7 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
     a.k_steps = (d->in_features + BK - 1) / BK;
     const int grid_o = (d->out_features + BM - 1) / BM;
     const int grid_m = (M + BN - 1) / BN;
+    if (BN == 512) return launch<512>(mi, mx, a, grid_m, grid_o, stream);
     if (BN == 256) return launch<256>(mi, mx, a, grid_m, grid_o, stream);
     if (BN == 128) return launch<128>(mi, mx, a, grid_m, grid_o, stream);
     return launch<64>(mi, mx, a, grid_m, grid_o, stream);

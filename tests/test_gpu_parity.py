@@ -270,7 +270,7 @@ GEMM_SHAPES = [  # (OUT, IN, G, col0)
 
 
 @pytest.mark.parametrize("shape", GEMM_SHAPES)
-@pytest.mark.parametrize("M", [17, 64, 100, 256, 300])
+@pytest.mark.parametrize("M", [17, 64, 100, 256, 300, 600])
 def test_gemm_vs_oracle(shape, M):
     n_out, n_in, G, col0 = shape
     rng = np.random.default_rng(n_out * 31 + n_in + M)
