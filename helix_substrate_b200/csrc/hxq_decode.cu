@@ -59,7 +59,81 @@ __device__ __forceinline__ float block_sum(float v, float* red) {   // blockDim.
 }
 
 // h[b,:] += delta[b,:] (bf16 add, skipped when delta == nullptr); out[b,:] = bf16(bf16(h * rsqrt(mean(h^2) + eps)) * w).
-// One CTA per row, 8 elements per thread per step.
+// One CTA per row.  Vector form: H % 8 == 0, 16-byte aligned rows, H <= 8 * 256 * kRmsVec: every thread
+// issues all its loads (h, delta, w) before it touches any of them, so the row costs one memory round trip.
+constexpr int kRmsVec = 6;
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        f[2 * e] = __uint_as_float(w[e] << 16);
+        f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+        w[e] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                                                              const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                                              int H, int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps) {
+    __shared__ float red[32];
+    pdl_enter();
+    const int nvec = H >> 3;
+    uint4* hp = reinterpret_cast<uint4*>(h + (int64_t)blockIdx.x * ld_h);
+    const uint4* dp = delta ? reinterpret_cast<const uint4*>(delta + (int64_t)blockIdx.x * ld_delta) : nullptr;
+    const uint4* wp = reinterpret_cast<const uint4*>(w);
+    uint4 hv[kRmsVec], dv[kRmsVec], wv[kRmsVec];
+#pragma unroll
+    for (int j = 0; j < kRmsVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        hv[j] = dv[j] = wv[j] = make_uint4(0, 0, 0, 0);
+        if (i < nvec) {
+            hv[j] = hp[i];
+            if (dp) dv[j] = dp[i];
+            wv[j] = wp[i];
+        }
+    }
+    float x[kRmsVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRmsVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        float d[8];
+        unpack8(hv[j], x[j]);
+        unpack8(dv[j], d);
+        if (dp) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[j][e] = bf(to_bf(x[j][e] + d[e]));
+            if (i < nvec) hp[i] = pack8(x[j]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[j][e] * x[j][e];
+    }
+    const float tot = block_sum(ss, red);
+    const float rs = rsqrtf(tot / (float)H + eps);
+    uint4* op = reinterpret_cast<uint4*>(out + (int64_t)blockIdx.x * ld_out);
+#pragma unroll
+    for (int j = 0; j < kRmsVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < nvec) {
+            float wf[8], o[8];
+            unpack8(wv[j], wf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = bf(to_bf(x[j][e] * rs)) * wf[e];
+            op[i] = pack8(o);
+        }
+    }
+}
+
+// Any H (<= 12000) and alignment: element-wise, the row kept in shared memory.
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
                                                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
                                                           int H, int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps) {
@@ -135,20 +209,35 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
     const int n_valid = (int)((pos - p0 + 1 < kAttnChunk) ? pos - p0 + 1 : kAttnChunk);
 
     __shared__ __align__(16) float q_s[kAttnMaxGroup][kAttnMaxD];
-    __shared__ __align__(16) __nv_bfloat16 kv_s[kAttnChunk][kAttnMaxD + 8];   // +16 B per row: rows start in different banks
+    __shared__ __align__(16) __nv_bfloat16 k_s[kAttnChunk][kAttnMaxD + 8];   // +16 B per row: rows start in different banks
+    __shared__ __align__(16) __nv_bfloat16 v_s[kAttnChunk][kAttnMaxD + 8];
     __shared__ float s_s[kAttnMaxGroup][kAttnChunk];
     __shared__ float m_s[kAttnMaxGroup], l_s[kAttnMaxGroup];
 
-    for (int i = t; i < G * D; i += kAttnThreads) {
-        const int g = i / D, d = i - g * D;
-        q_s[g][d] = bf(q[(int64_t)b * ld_q + (int64_t)(kvh * G + g) * D + d]) * scale;
-    }
+    // K tile, then V tile, as two asynchronous copy groups: V lands while the scores are computed
     const int64_t base = (((int64_t)b * nkv + kvh) * max_len + p0) * D;
     const int vec_per_row = D / 8;    // 16-byte pieces per row
     for (int i = t; i < n_valid * vec_per_row; i += kAttnThreads) {
         const int r = i / vec_per_row, v = i - r * vec_per_row;
-        *reinterpret_cast<uint4*>(&kv_s[r][v * 8]) = *reinterpret_cast<const uint4*>(k_cache + base + (int64_t)r * D + v * 8);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(&k_s[r][v * 8])),
+                     "l"(k_cache + base + (int64_t)r * D + v * 8) : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = t; i < n_valid * vec_per_row; i += kAttnThreads) {
+        const int r = i / vec_per_row, v = i - r * vec_per_row;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(&v_s[r][v * 8])),
+                     "l"(v_cache + base + (int64_t)r * D + v * 8) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (t < G * vec_per_row) {   // G * D / 8 <= 128 vectors of q
+        const int g = t / vec_per_row, d = (t - g * vec_per_row) * 8;
+        const uint4 qv = *reinterpret_cast<const uint4*>(q + (int64_t)b * ld_q + (int64_t)(kvh * G + g) * D + d);
+        float f[8];
+        unpack8(qv, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q_s[g][d + e] = f[e] * scale;
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
 
     // scores: thread (p = t % 64, hg = t / 64) takes query heads hg, hg + 2, ... of position p
@@ -159,7 +248,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
         for (int j = 0; j < kAttnMaxGroup / 2; ++j) acc[j] = 0.f;
         if (p < n_valid) {
             for (int d = 0; d < D; d += 8) {
-                const uint4 kk = *reinterpret_cast<const uint4*>(&kv_s[p][d]);
+                const uint4 kk = *reinterpret_cast<const uint4*>(&k_s[p][d]);
                 const uint32_t w[4] = {kk.x, kk.y, kk.z, kk.w};
                 float kf[8];
 #pragma unroll
@@ -187,11 +276,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
     }
     __syncthreads();
 
-    // V over K's buffer (everyone is done with K), softmax pieces per head meanwhile
-    for (int i = t; i < n_valid * vec_per_row; i += kAttnThreads) {
-        const int r = i / vec_per_row, v = i - r * vec_per_row;
-        *reinterpret_cast<uint4*>(&kv_s[r][v * 8]) = *reinterpret_cast<const uint4*>(v_cache + base + (int64_t)r * D + v * 8);
-    }
+    // softmax pieces per head
     {
         const int warp = t >> 5, lane = t & 31;
         for (int g = warp; g < G; g += kAttnThreads / 32) {
@@ -208,6 +293,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
             if (lane == 0) { m_s[g] = m; l_s[g] = l; }
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
 
     // o[g][d] = sum_p prob[g][p] * V[p][d]; thread t owns dimension d = t (and d + 128 ... if D > 128: not supported)
@@ -216,7 +302,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
 #pragma unroll
         for (int g = 0; g < kAttnMaxGroup; ++g) o[g] = 0.f;
         for (int p = 0; p < n_valid; ++p) {
-            const float v = bf(kv_s[p][t]);
+            const float v = bf(v_s[p][t]);
 #pragma unroll
             for (int g = 0; g < kAttnMaxGroup; ++g)
                 if (g < G) o[g] += s_s[g][p] * v;
@@ -232,23 +318,52 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
 }
 
 // out[b, head, :] = sum_c exp(m_c - M) o_c / sum_c exp(m_c - M) l_c over the chunks up to the position.
+// The chunk weights are computed by the block together (dynamic shared memory: n_chunks floats);
+// thread t then adds up dimension t with independent loads.
 __global__ void __launch_bounds__(kAttnMaxD) attn_combine_kernel(const float* __restrict__ part, const int64_t* __restrict__ pos_p,
                                                                 __nv_bfloat16* __restrict__ out, int64_t ld_out,
                                                                 int nq, int D, int max_len, int n_chunks) {
+    extern __shared__ float w_s[];   // [n_chunks]
+    __shared__ float red[32];
     const int head = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
     pdl_enter();
     const int64_t pos = *pos_p;
-    if (pos < 0 || pos >= max_len || t >= D) return;
+    if (pos < 0 || pos >= max_len) return;
     const int nc = (int)(pos / kAttnChunk) + 1;
     const float* src = part + ((int64_t)b * nq + head) * n_chunks * (D + 2);
-    float M = -INFINITY;
-    for (int c = 0; c < nc; ++c) M = fmaxf(M, src[c * (D + 2)]);
-    float L = 0.f, o = 0.f;
-    for (int c = 0; c < nc; ++c) {
-        const float w = __expf(src[c * (D + 2)] - M);
-        L += w * src[c * (D + 2) + 1];
-        o += w * src[c * (D + 2) + 2 + t];
+    float mx = -INFINITY;
+    for (int c = t; c < nc; c += kAttnMaxD) {
+        const float m = src[c * (D + 2)];
+        w_s[c] = m;
+        mx = fmaxf(mx, m);
     }
+    {   // block max
+        const int lane = t & 31, warp = t >> 5;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red[warp] = mx;
+        __syncthreads();
+        mx = red[0];
+#pragma unroll
+        for (int i = 1; i < kAttnMaxD / 32; ++i) mx = fmaxf(mx, red[i]);
+        __syncthreads();
+    }
+    float ls = 0.f;
+    for (int c = t; c < nc; c += kAttnMaxD) {
+        const float wgt = __expf(w_s[c] - mx);
+        w_s[c] = wgt;
+        ls += wgt * src[c * (D + 2) + 1];
+    }
+    const float L = block_sum(ls, red);   // also makes w_s visible to everyone
+    if (t >= D) return;
+    float o = 0.f;
+    int c = 0;
+    for (; c + 4 <= nc; c += 4) {
+        const float a0 = src[(c + 0) * (D + 2) + 2 + t], a1 = src[(c + 1) * (D + 2) + 2 + t];
+        const float a2 = src[(c + 2) * (D + 2) + 2 + t], a3 = src[(c + 3) * (D + 2) + 2 + t];
+        o += w_s[c] * a0 + w_s[c + 1] * a1 + w_s[c + 2] * a2 + w_s[c + 3] * a3;
+    }
+    for (; c < nc; ++c) o += w_s[c] * src[c * (D + 2) + 2 + t];
     out[(int64_t)b * ld_out + (int64_t)head * D + t] = to_bf(o / L);
 }
 
@@ -280,8 +395,12 @@ using namespace hxq::dec;
 extern "C" int hxq_add_rmsnorm(void* h, const void* delta, const void* weight, void* out, int32_t B, int32_t H,
                                int64_t ld_h, int64_t ld_delta, int64_t ld_out, float eps, hxq_stream_t stream) {
     if (!h || !weight || !out || B <= 0 || H <= 0) return HXQ_E_ARG;
-    if (H > 12000) return HXQ_E_SHAPE;   // the row is kept in shared memory
-    const cudaError_t e = launch_pdl(add_rmsnorm_kernel, dim3(B), dim3(256), H * sizeof(float), reinterpret_cast<cudaStream_t>(stream),
+    if (H > 12000) return HXQ_E_SHAPE;   // the row is kept in registers / shared memory
+    const bool vec = (H % 8 == 0) && H <= 8 * 256 * kRmsVec && hxq::aligned_to(h, 16) && hxq::aligned_to(out, 16) &&
+                     hxq::aligned_to(weight, 16) && (!delta || hxq::aligned_to(delta, 16)) && ld_h % 8 == 0 &&
+                     ld_out % 8 == 0 && (!delta || ld_delta % 8 == 0);
+    const cudaError_t e = launch_pdl(vec ? add_rmsnorm_vec_kernel : add_rmsnorm_kernel, dim3(B), dim3(256),
+                                     vec ? 0 : H * sizeof(float), reinterpret_cast<cudaStream_t>(stream),
         reinterpret_cast<__nv_bfloat16*>(h), reinterpret_cast<const __nv_bfloat16*>(delta),
         reinterpret_cast<const __nv_bfloat16*>(weight), reinterpret_cast<__nv_bfloat16*>(out), (int)H, ld_h, ld_delta, ld_out, eps);
     return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
@@ -310,7 +429,8 @@ extern "C" int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache,
                                int32_t nkv, int32_t D, int32_t max_len, float scale, hxq_stream_t stream) {
     if (!q || !k_cache || !v_cache || !pos || !out) return HXQ_E_ARG;
     if (B <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > kAttnMaxGroup) return HXQ_E_SHAPE;
-    if (D <= 0 || D > kAttnMaxD || D % 8 != 0 || max_len <= 0) return HXQ_E_SHAPE;
+    if (D <= 0 || D > kAttnMaxD || D % 8 != 0 || max_len <= 0 || max_len > 64 * 8192) return HXQ_E_SHAPE;
+    if (!hxq::aligned_to(q, 16) || ld_q % 8 != 0) return HXQ_E_ALIGN;
     if (!hxq::aligned_to(k_cache, 16) || !hxq::aligned_to(v_cache, 16)) return HXQ_E_ALIGN;
     if (!workspace || workspace_bytes < hxq_attn_decode_workspace_bytes(B, nq, D, max_len)) return HXQ_E_WORKSPACE;
     const int n_chunks = (max_len + kAttnChunk - 1) / kAttnChunk;
@@ -320,7 +440,7 @@ extern "C" int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache,
                    reinterpret_cast<const __nv_bfloat16*>(v_cache), pos, reinterpret_cast<float*>(workspace), (int)nq, (int)nkv,
                    (int)D, (int)max_len, n_chunks, scale) != cudaSuccess)
         return HXQ_E_LAUNCH;
-    const cudaError_t e = launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(kAttnMaxD), 0, s,
+    const cudaError_t e = launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(kAttnMaxD), n_chunks * sizeof(float), s,
                                      reinterpret_cast<const float*>(workspace), pos, reinterpret_cast<__nv_bfloat16*>(out), ld_out,
                                      (int)nq, (int)D, (int)max_len, n_chunks);
     return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;

@@ -16,7 +16,7 @@ def _dev():
     return torch.device("cuda:0")
 
 
-@pytest.mark.parametrize("B,H,with_delta", [(1, 3584, True), (4, 256, True), (2, 5120, False), (3, 1000, True)])
+@pytest.mark.parametrize("B,H,with_delta", [(1, 3584, True), (4, 256, True), (2, 5120, False), (3, 1000, True), (2, 1001, True), (1, 11000, True)])
 def test_add_rmsnorm(B, H, with_delta):
     from helix_substrate_b200 import decode_ops
     g = torch.Generator(device=_dev()).manual_seed(B * 1000 + H)
