@@ -318,53 +318,72 @@ __global__ void __launch_bounds__(kAttnThreads) attn_partial_kernel(const __nv_b
 }
 
 // out[b, head, :] = sum_c exp(m_c - M) o_c / sum_c exp(m_c - M) l_c over the chunks up to the position.
-// The chunk weights are computed by the block together (dynamic shared memory: n_chunks floats);
-// thread t then adds up dimension t with independent loads.
-__global__ void __launch_bounds__(kAttnMaxD) attn_combine_kernel(const float* __restrict__ part, const int64_t* __restrict__ pos_p,
-                                                                __nv_bfloat16* __restrict__ out, int64_t ld_out,
-                                                                int nq, int D, int max_len, int n_chunks) {
+// 4 x 128 threads: the chunk weights are computed by the block together (dynamic shared memory:
+// n_chunks floats); thread (d, j) then adds up dimension d over chunks j, j + 4, ... eight
+// independent loads at a time, and the four partial sums meet in shared memory.
+constexpr int kCombineGroups = 4;
+constexpr int kCombineThreads = kCombineGroups * kAttnMaxD;
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    __syncthreads();
+    return t;
+}
+
+__global__ void __launch_bounds__(kCombineThreads) attn_combine_kernel(const float* __restrict__ part, const int64_t* __restrict__ pos_p,
+                                                                      __nv_bfloat16* __restrict__ out, int64_t ld_out,
+                                                                      int nq, int D, int max_len, int n_chunks) {
     extern __shared__ float w_s[];   // [n_chunks]
     __shared__ float red[32];
-    const int head = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    __shared__ float o_s[kCombineGroups][kAttnMaxD];
+    const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int d = tid & (kAttnMaxD - 1), j = tid / kAttnMaxD;
     pdl_enter();
     const int64_t pos = *pos_p;
     if (pos < 0 || pos >= max_len) return;
     const int nc = (int)(pos / kAttnChunk) + 1;
     const float* src = part + ((int64_t)b * nq + head) * n_chunks * (D + 2);
     float mx = -INFINITY;
-    for (int c = t; c < nc; c += kAttnMaxD) {
+    for (int c = tid; c < nc; c += kCombineThreads) {
         const float m = src[c * (D + 2)];
         w_s[c] = m;
         mx = fmaxf(mx, m);
     }
-    {   // block max
-        const int lane = t & 31, warp = t >> 5;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red[warp] = mx;
-        __syncthreads();
-        mx = red[0];
-#pragma unroll
-        for (int i = 1; i < kAttnMaxD / 32; ++i) mx = fmaxf(mx, red[i]);
-        __syncthreads();
-    }
+    mx = block_max(mx, red);
     float ls = 0.f;
-    for (int c = t; c < nc; c += kAttnMaxD) {
+    for (int c = tid; c < nc; c += kCombineThreads) {
         const float wgt = __expf(w_s[c] - mx);
         w_s[c] = wgt;
         ls += wgt * src[c * (D + 2) + 1];
     }
     const float L = block_sum(ls, red);   // also makes w_s visible to everyone
-    if (t >= D) return;
     float o = 0.f;
-    int c = 0;
-    for (; c + 4 <= nc; c += 4) {
-        const float a0 = src[(c + 0) * (D + 2) + 2 + t], a1 = src[(c + 1) * (D + 2) + 2 + t];
-        const float a2 = src[(c + 2) * (D + 2) + 2 + t], a3 = src[(c + 3) * (D + 2) + 2 + t];
-        o += w_s[c] * a0 + w_s[c + 1] * a1 + w_s[c + 2] * a2 + w_s[c + 3] * a3;
+    if (d < D) {
+        for (int c0 = j; c0 < nc; c0 += kCombineGroups * 8) {
+            float a[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c = c0 + k * kCombineGroups;
+                a[k] = (c < nc) ? src[c * (D + 2) + 2 + d] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c = c0 + k * kCombineGroups;
+                if (c < nc) o += w_s[c] * a[k];
+            }
+        }
     }
-    for (; c < nc; ++c) o += w_s[c] * src[c * (D + 2) + 2 + t];
-    out[(int64_t)b * ld_out + (int64_t)head * D + t] = to_bf(o / L);
+    o_s[j][d] = o;
+    __syncthreads();
+    if (j == 0 && d < D)
+        out[(int64_t)b * ld_out + (int64_t)head * D + d] = to_bf((o_s[0][d] + o_s[1][d] + o_s[2][d] + o_s[3][d]) / L);
 }
 
 // out = bf16(bf16(silu(gate)) * up), element-wise over [B, n].
@@ -440,7 +459,7 @@ extern "C" int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache,
                    reinterpret_cast<const __nv_bfloat16*>(v_cache), pos, reinterpret_cast<float*>(workspace), (int)nq, (int)nkv,
                    (int)D, (int)max_len, n_chunks, scale) != cudaSuccess)
         return HXQ_E_LAUNCH;
-    const cudaError_t e = launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(kAttnMaxD), n_chunks * sizeof(float), s,
+    const cudaError_t e = launch_pdl(attn_combine_kernel, dim3(nq, B), dim3(kCombineThreads), n_chunks * sizeof(float), s,
                                      reinterpret_cast<const float*>(workspace), pos, reinterpret_cast<__nv_bfloat16*>(out), ld_out,
                                      (int)nq, (int)D, (int)max_len, n_chunks);
     return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;

@@ -66,8 +66,21 @@ def _hxq_linear(out_f: int, in_f: int, seed: int, device, bias: bool, group_size
     return mod
 
 
+def _hxq_fused_columns(outs, in_f: int, seed: int, device, bias: bool, group_size: int, name: str,
+                       rank: int, world: int) -> HelixLinear:
+    """Several column-parallel projections of one input as ONE compressed matrix (rows concatenated,
+    one codebook): this rank's slice of each, generated at its local size."""
+    rows = sum(o // world for o in outs)
+    g = torch.Generator(device=device).manual_seed(seed * 64 + rank)
+    w = torch.randn(rows, in_f, device=device, generator=g) * 0.02
+    b = (torch.randn(rows, device=device, generator=g) * 0.02) if bias else None
+    enc = compress_weight(w, percentile=99.95, group_size=group_size)
+    del w
+    return HelixLinear(in_f, rows, bias=b, tensor_name=name, **enc)
+
+
 class Qwen2Layer(nn.Module):
-    def __init__(self, shp: Qwen2Shape, li: int, device, group_size: int, rank: int, world: int):
+    def __init__(self, shp: Qwen2Shape, li: int, device, group_size: int, rank: int, world: int, fuse: bool = True):
         super().__init__()
         H, D = shp.hidden, shp.head_dim
         if shp.heads % world or shp.kv_heads % world:
@@ -75,13 +88,21 @@ class Qwen2Layer(nn.Module):
         p = f"model.layers.{li}"
         mk = lambda o, i, k, bias, name, mode: _hxq_linear(o, i, 1000 * li + k, device, bias, group_size,
                                                            f"{p}.{name}.weight", mode, rank, world)
-        self.q_proj = mk(shp.heads * D, H, 0, True, "self_attn.q_proj", "column")
-        self.k_proj = mk(shp.kv_heads * D, H, 1, True, "self_attn.k_proj", "column")
-        self.v_proj = mk(shp.kv_heads * D, H, 2, True, "self_attn.v_proj", "column")
+        self.fused = fuse
+        if fuse:   # q|k|v and gate|up as one compressed matrix each: 4 products per layer instead of 7
+            self.qkv_proj = _hxq_fused_columns([shp.heads * D, shp.kv_heads * D, shp.kv_heads * D], H, 1000 * li + 7,
+                                               device, True, group_size, f"{p}.self_attn.qkv_proj.weight", rank, world)
+            self.gate_up_proj = _hxq_fused_columns([shp.inter, shp.inter], H, 1000 * li + 8, device, False, group_size,
+                                                   f"{p}.mlp.gate_up_proj.weight", rank, world)
+        else:
+            self.q_proj = mk(shp.heads * D, H, 0, True, "self_attn.q_proj", "column")
+            self.k_proj = mk(shp.kv_heads * D, H, 1, True, "self_attn.k_proj", "column")
+            self.v_proj = mk(shp.kv_heads * D, H, 2, True, "self_attn.v_proj", "column")
+            self.gate_proj = mk(shp.inter, H, 4, False, "mlp.gate_proj", "column")
+            self.up_proj = mk(shp.inter, H, 5, False, "mlp.up_proj", "column")
         self.o_proj = mk(H, shp.heads * D, 3, False, "self_attn.o_proj", "row")
-        self.gate_proj = mk(shp.inter, H, 4, False, "mlp.gate_proj", "column")
-        self.up_proj = mk(shp.inter, H, 5, False, "mlp.up_proj", "column")
         self.down_proj = mk(H, shp.inter, 6, False, "mlp.down_proj", "row")
+        self.inter_local = shp.inter // world
         self.ln1 = nn.Parameter(torch.ones(H, device=device, dtype=torch.bfloat16), requires_grad=False)
         self.ln2 = nn.Parameter(torch.ones(H, device=device, dtype=torch.bfloat16), requires_grad=False)
         self.n_q, self.n_kv = shp.heads // world, shp.kv_heads // world
@@ -92,10 +113,11 @@ class Qwen2HxqDecoder(nn.Module):
     ``step`` decodes one token per sequence at ``pos`` (a device scalar)."""
 
     def __init__(self, shp: Qwen2Shape, device, batch: int, max_len: int, group_size: int = 128,
-                 rank: int = 0, world: int = 1, group=None):
+                 rank: int = 0, world: int = 1, group=None, fuse_proj: bool = True):
         super().__init__()
         self.shp, self.device, self.world, self.group = shp, device, world, group
-        self.layers = nn.ModuleList(Qwen2Layer(shp, i, device, group_size, rank, world) for i in range(shp.layers))
+        self.layers = nn.ModuleList(Qwen2Layer(shp, i, device, group_size, rank, world, fuse_proj)
+                                    for i in range(shp.layers))
         g = torch.Generator(device=device).manual_seed(7)
         self.embed = (torch.randn(shp.vocab, shp.hidden, device=device, generator=g) * 0.02).bfloat16()
         self.lm_head = (torch.randn(shp.vocab, shp.hidden, device=device, generator=g) * 0.02).bfloat16()
@@ -135,9 +157,13 @@ class Qwen2HxqDecoder(nn.Module):
         cos, sin = self.cos[positions][None, None], self.sin[positions][None, None]
         for li, L in enumerate(self.layers):
             x = self._rms(h, L.ln1)
-            q = L.q_proj(x).view(B, T, L.n_q, D).transpose(1, 2)
-            k = L.k_proj(x).view(B, T, L.n_kv, D).transpose(1, 2)
-            v = L.v_proj(x).view(B, T, L.n_kv, D).transpose(1, 2)
+            if L.fused:
+                q, k, v = L.qkv_proj(x).split([L.n_q * D, L.n_kv * D, L.n_kv * D], -1)
+            else:
+                q, k, v = L.q_proj(x), L.k_proj(x), L.v_proj(x)
+            q = q.reshape(B, T, L.n_q, D).transpose(1, 2)
+            k = k.reshape(B, T, L.n_kv, D).transpose(1, 2)
+            v = v.reshape(B, T, L.n_kv, D).transpose(1, 2)
             q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
             self.k_cache[li].index_copy_(2, cache_rows, k)
             self.v_cache[li].index_copy_(2, cache_rows, v)
@@ -151,7 +177,11 @@ class Qwen2HxqDecoder(nn.Module):
             a = a.transpose(1, 2).reshape(B, T, L.n_q * D)
             h = h + self._allreduce(L.o_proj(a))
             x = self._rms(h, L.ln2)
-            h = h + self._allreduce(L.down_proj(F.silu(L.gate_proj(x)) * L.up_proj(x)))
+            if L.fused:
+                gt, up = L.gate_up_proj(x).split([L.inter_local, L.inter_local], -1)
+            else:
+                gt, up = L.gate_proj(x), L.up_proj(x)
+            h = h + self._allreduce(L.down_proj(F.silu(gt) * up))
         h = self._rms(h[:, -1], self.norm)
         return h @ self.lm_head.t()
 
@@ -161,8 +191,7 @@ class Qwen2HxqDecoder(nn.Module):
             L0, D, dev = self.layers[0], self.shp.head_dim, self.device
             mk = lambda n: torch.empty(B, n, device=dev, dtype=torch.bfloat16)
             sb = dict(h=mk(self.shp.hidden), x=mk(self.shp.hidden), qkv=mk((L0.n_q + 2 * L0.n_kv) * D),
-                      q=mk(L0.n_q * D), a=mk(L0.n_q * D), g=mk(L0.gate_proj.out_features),
-                      u=mk(L0.gate_proj.out_features), act=mk(L0.gate_proj.out_features),
+                      q=mk(L0.n_q * D), a=mk(L0.n_q * D), gu=mk(2 * L0.inter_local), act=mk(L0.inter_local),
                       d1=mk(self.shp.hidden), d2=mk(self.shp.hidden))
             self._sb = sb
         return sb
@@ -181,17 +210,23 @@ class Qwen2HxqDecoder(nn.Module):
         for li, L in enumerate(self.layers):
             nq, nkv = L.n_q, L.n_kv
             decode_ops.add_rmsnorm(h, delta, L.ln1, eps, x)
-            qkv = sb["qkv"]
-            L.q_proj.packed().matmul(x, bf, out=qkv[:, : nq * D])
-            L.k_proj.packed().matmul(x, bf, out=qkv[:, nq * D: (nq + nkv) * D])
-            L.v_proj.packed().matmul(x, bf, out=qkv[:, (nq + nkv) * D:])
+            qkv, gu, ni = sb["qkv"], sb["gu"], L.inter_local
+            if L.fused:
+                L.qkv_proj.packed().matmul(x, bf, out=qkv)
+            else:
+                L.q_proj.packed().matmul(x, bf, out=qkv[:, : nq * D])
+                L.k_proj.packed().matmul(x, bf, out=qkv[:, nq * D: (nq + nkv) * D])
+                L.v_proj.packed().matmul(x, bf, out=qkv[:, (nq + nkv) * D:])
             decode_ops.rope_append(qkv, pos, self.cos, self.sin, sb["q"], self.k_cache[li], self.v_cache[li], nq, nkv)
             decode_ops.attn_decode(sb["q"], self.k_cache[li], self.v_cache[li], pos, sb["a"], nq, D ** -0.5)
             delta = self._allreduce(L.o_proj.packed().matmul(sb["a"], bf, out=sb["d1"]))
             decode_ops.add_rmsnorm(h, delta, L.ln2, eps, x)
-            L.gate_proj.packed().matmul(x, bf, out=sb["g"])
-            L.up_proj.packed().matmul(x, bf, out=sb["u"])
-            decode_ops.swiglu(sb["g"], sb["u"], sb["act"])
+            if L.fused:
+                L.gate_up_proj.packed().matmul(x, bf, out=gu)
+            else:
+                L.gate_proj.packed().matmul(x, bf, out=gu[:, :ni])
+                L.up_proj.packed().matmul(x, bf, out=gu[:, ni:])
+            decode_ops.swiglu(gu[:, :ni], gu[:, ni:], sb["act"])
             delta = self._allreduce(L.down_proj.packed().matmul(sb["act"], bf, out=sb["d2"]))
         decode_ops.add_rmsnorm(h, delta, self.norm, eps, x)
         return x @ self.lm_head.t()
@@ -272,6 +307,8 @@ def main(argv=None):
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--torch-glue", action="store_true", help="run the step's glue in plain torch ops")
+    ap.add_argument("--separate-proj", action="store_true",
+                    help="q, k, v and gate, up as separate compressed matrices (7 products per layer instead of 4)")
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -284,7 +321,8 @@ def main(argv=None):
     if args.layers:
         shp.layers = args.layers
     t0 = time.perf_counter()
-    model = Qwen2HxqDecoder(shp, dev, args.batch, args.prompt + args.new + 8, rank=rank, world=world)
+    model = Qwen2HxqDecoder(shp, dev, args.batch, args.prompt + args.new + 8, rank=rank, world=world,
+                            fuse_proj=not args.separate_proj)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     prompt = torch.randint(0, shp.vocab, (args.batch, args.prompt), device=dev,
@@ -325,6 +363,7 @@ def main(argv=None):
             "ms_per_token_step": ms_dec, "batch": args.batch, "prompt": args.prompt, "new_tokens": args.new,
             "shape": args.shape, "layers": shp.layers, "n_gpus": world, "launch": "python" if run is None else "cuda_graph",
             "glue": "torch" if (args.torch_glue or run is None) else "fused",
+            "projections": "q,k,v,o,gate,up,down" if args.separate_proj else "qkv,o,gate_up,down",
             "hxq_algorithmic_bytes_per_step_per_gpu": hxq_bytes,
             "hxq_GBps_per_gpu_if_all_time_were_linears": hxq_bytes / (ms_dec * 1e-3) / 1e9,
             "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,

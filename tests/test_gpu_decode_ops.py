@@ -104,11 +104,12 @@ def test_glue_rejects_bad_arguments():
         decode_ops.attn_decode(q, kc, kc, torch.zeros(1, device=_dev(), dtype=torch.long), torch.empty_like(q), 9, 0.125)
 
 
-def test_fused_step_matches_the_torch_step():
+@pytest.mark.parametrize("fuse_proj", [True, False])
+def test_fused_step_matches_the_torch_step(fuse_proj):
     from helix_substrate_b200.qwen2_decode import Qwen2HxqDecoder, Qwen2Shape
     dev = _dev()
     torch.manual_seed(0)
-    model = Qwen2HxqDecoder(Qwen2Shape.tiny(), dev, batch=2, max_len=96)
+    model = Qwen2HxqDecoder(Qwen2Shape.tiny(), dev, batch=2, max_len=96, fuse_proj=fuse_proj)
     prompt = torch.randint(0, 1024, (2, 70), device=dev)
     with torch.no_grad():
         nxt = model.prefill(prompt)
