@@ -90,6 +90,13 @@ def lib() -> C.CDLL:
     L.hxq_swiglu.restype = C.c_int
     L.hxq_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                              C.c_int64, C.c_void_p]
+    L.hxq_allreduce_buffer_bytes.restype = C.c_size_t
+    L.hxq_allreduce_buffer_bytes.argtypes = [C.c_int32, C.c_int64]
+    L.hxq_allreduce_flag_bytes.restype = C.c_size_t
+    L.hxq_allreduce_flag_bytes.argtypes = [C.c_int32]
+    L.hxq_allreduce_oneshot.restype = C.c_int
+    L.hxq_allreduce_oneshot.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
+                                        C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
     _lib = L
     return L
 

@@ -113,9 +113,10 @@ class Qwen2HxqDecoder(nn.Module):
     ``step`` decodes one token per sequence at ``pos`` (a device scalar)."""
 
     def __init__(self, shp: Qwen2Shape, device, batch: int, max_len: int, group_size: int = 128,
-                 rank: int = 0, world: int = 1, group=None, fuse_proj: bool = True):
+                 rank: int = 0, world: int = 1, group=None, fuse_proj: bool = True, p2p_allreduce: bool = False):
         super().__init__()
         self.shp, self.device, self.world, self.group = shp, device, world, group
+        self.p2p = bool(p2p_allreduce) and world > 1   # one-shot peer-memory sum instead of NCCL in the fused step
         self.layers = nn.ModuleList(Qwen2Layer(shp, i, device, group_size, rank, world, fuse_proj)
                                     for i in range(shp.layers))
         g = torch.Generator(device=device).manual_seed(7)
@@ -193,8 +194,19 @@ class Qwen2HxqDecoder(nn.Module):
             sb = dict(h=mk(self.shp.hidden), x=mk(self.shp.hidden), qkv=mk((L0.n_q + 2 * L0.n_kv) * D),
                       q=mk(L0.n_q * D), a=mk(L0.n_q * D), gu=mk(2 * L0.inter_local), act=mk(L0.inter_local),
                       d1=mk(self.shp.hidden), d2=mk(self.shp.hidden))
+            if self.p2p:
+                from .tp import OneShotAllReduce
+                sb["p32"] = torch.empty(B, self.shp.hidden, device=dev, dtype=torch.float32)
+                self._ar = OneShotAllReduce(B * self.shp.hidden, dev, self.group)
             self._sb = sb
         return sb
+
+    def _row_parallel(self, lin: HelixLinear, x: torch.Tensor, sb: dict, out_key: str) -> torch.Tensor:
+        """Row-parallel product + the sum over ranks, result in bf16 in sb[out_key]."""
+        if self.p2p:
+            lin.packed().matmul(x, torch.float32, out=sb["p32"])
+            return self._ar(sb["p32"], out=sb[out_key])
+        return self._allreduce(lin.packed().matmul(x, torch.bfloat16, out=sb[out_key]))
 
     def step_fused(self, tok: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         """One decode step for tok [B, 1] at position pos (int64 device tensor [1]): same
@@ -219,7 +231,7 @@ class Qwen2HxqDecoder(nn.Module):
                 L.v_proj.packed().matmul(x, bf, out=qkv[:, (nq + nkv) * D:])
             decode_ops.rope_append(qkv, pos, self.cos, self.sin, sb["q"], self.k_cache[li], self.v_cache[li], nq, nkv)
             decode_ops.attn_decode(sb["q"], self.k_cache[li], self.v_cache[li], pos, sb["a"], nq, D ** -0.5)
-            delta = self._allreduce(L.o_proj.packed().matmul(sb["a"], bf, out=sb["d1"]))
+            delta = self._row_parallel(L.o_proj, sb["a"], sb, "d1")
             decode_ops.add_rmsnorm(h, delta, L.ln2, eps, x)
             if L.fused:
                 L.gate_up_proj.packed().matmul(x, bf, out=gu)
@@ -227,7 +239,7 @@ class Qwen2HxqDecoder(nn.Module):
                 L.gate_proj.packed().matmul(x, bf, out=gu[:, :ni])
                 L.up_proj.packed().matmul(x, bf, out=gu[:, ni:])
             decode_ops.swiglu(gu[:, :ni], gu[:, ni:], sb["act"])
-            delta = self._allreduce(L.down_proj.packed().matmul(sb["act"], bf, out=sb["d2"]))
+            delta = self._row_parallel(L.down_proj, sb["act"], sb, "d2")
         decode_ops.add_rmsnorm(h, delta, self.norm, eps, x)
         return x @ self.lm_head.t()
 
@@ -307,6 +319,8 @@ def main(argv=None):
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--torch-glue", action="store_true", help="run the step's glue in plain torch ops")
+    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "p2p"],
+                    help="tensor-parallel sum in the fused step: NCCL, or the one-shot peer-memory kernel")
     ap.add_argument("--separate-proj", action="store_true",
                     help="q, k, v and gate, up as separate compressed matrices (7 products per layer instead of 4)")
     args = ap.parse_args(argv)
@@ -322,7 +336,7 @@ def main(argv=None):
         shp.layers = args.layers
     t0 = time.perf_counter()
     model = Qwen2HxqDecoder(shp, dev, args.batch, args.prompt + args.new + 8, rank=rank, world=world,
-                            fuse_proj=not args.separate_proj)
+                            fuse_proj=not args.separate_proj, p2p_allreduce=args.allreduce == "p2p")
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     prompt = torch.randint(0, shp.vocab, (args.batch, args.prompt), device=dev,
@@ -364,6 +378,7 @@ def main(argv=None):
             "shape": args.shape, "layers": shp.layers, "n_gpus": world, "launch": "python" if run is None else "cuda_graph",
             "glue": "torch" if (args.torch_glue or run is None) else "fused",
             "projections": "q,k,v,o,gate,up,down" if args.separate_proj else "qkv,o,gate_up,down",
+            "allreduce": (args.allreduce if world > 1 else None),
             "hxq_algorithmic_bytes_per_step_per_gpu": hxq_bytes,
             "hxq_GBps_per_gpu_if_all_time_were_linears": hxq_bytes / (ms_dec * 1e-3) / 1e9,
             "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,

@@ -102,3 +102,84 @@ class RowParallelHelixLinear(nn.Module):
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
+
+
+class OneShotAllReduce:
+    """Sum of fp32 partials over the tensor-parallel ranks of one node for decode-sized
+    messages (up to 131072 elements): one kernel per rank over peer memory
+    (``hxq_allreduce_oneshot``), result in bf16, identical on every rank.
+
+    The receive buffers are symmetric memory (``torch.distributed._symmetric_memory``): the
+    same allocation on every GPU, mapped into every process.  ``local_emulation`` builds the
+    same object from plain tensors of ONE GPU, for tests that play the other ranks by
+    writing their partials and flags into this rank's buffer before the call."""
+
+    def __init__(self, n_max: int, device, group=None, wait_ms: float = 1000.0):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self._setup_sizes(n_max)
+        self.mem = symm.empty(self._nbuf + self._nflag, dtype=torch.uint8, device=device)
+        self.mem.zero_()
+        hdl = symm.rendezvous(self.mem, group=group)
+        self._finish([int(p) for p in hdl.buffer_ptrs], device, wait_ms)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)      # nobody pushes before everybody's buffer is zero
+
+    def _setup_sizes(self, n_max: int) -> None:
+        from . import _lib
+        L = _lib.lib()
+        self.n_max = -(-int(n_max) // 8) * 8
+        self._nbuf = L.hxq_allreduce_buffer_bytes(self.world, self.n_max)
+        self._nflag = L.hxq_allreduce_flag_bytes(self.world)
+        if self._nbuf == 0 or self._nflag == 0:
+            raise ValueError(f"unsupported world size {self.world} (1..8) or message size {n_max}")
+
+    def _finish(self, ptrs, device, wait_ms: float) -> None:
+        import ctypes as C
+        self._bufs = (C.c_void_p * self.world)(*ptrs)
+        self._flags = (C.c_void_p * self.world)(*[p + self._nbuf for p in ptrs])
+        self.counters = torch.zeros(32, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.wait_cycles = int(wait_ms * 1.9e6)
+        self.device = device
+
+    @classmethod
+    def local_emulation(cls, world: int, rank: int, n_max: int, device, wait_ms: float = 1000.0):
+        self = cls.__new__(cls)
+        self.world, self.rank = world, rank
+        self._setup_sizes(n_max)
+        self.mems = [torch.zeros(self._nbuf + self._nflag, dtype=torch.uint8, device=device) for _ in range(world)]
+        self.mem = self.mems[rank]
+        self._finish([m.data_ptr() for m in self.mems], device, wait_ms)
+        return self
+
+    def views(self, r: int = None):
+        """(partials fp32 [2, world, n_max], flags int32 [2, world, 32]) of rank r's buffer
+        (only ``local_emulation`` can look at other ranks')."""
+        mem = self.mem if r is None or r == self.rank else self.mems[r]
+        return (mem[: self._nbuf].view(torch.float32).view(2, self.world, self.n_max),
+                mem[self._nbuf:].view(torch.int32).view(2, self.world, 32))
+
+    def __call__(self, partial: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        import ctypes as C
+        from . import _lib
+        assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous()
+        n = partial.numel()
+        if out is None:
+            out = torch.empty(partial.shape, dtype=torch.bfloat16, device=partial.device)
+        assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == n
+        with torch.cuda.device(self.device):
+            st = _lib.lib().hxq_allreduce_oneshot(
+                self._bufs, self._flags, self.rank, self.world, self.n_max, C.c_void_p(partial.data_ptr()),
+                C.c_void_p(out.data_ptr()), n, C.c_void_p(self.counters.data_ptr()), self.wait_cycles,
+                C.c_void_p(self.status.data_ptr()), C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        _lib.check(st, "hxq_allreduce_oneshot")
+        return out
+
+    def check_status(self) -> int:
+        """0, or HXQ_E_TIMEOUT if a rank gave up waiting for the others (synchronises)."""
+        return int(self.status.item())
+

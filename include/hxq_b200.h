@@ -196,6 +196,31 @@ int hxq_swiglu(const void* gate, const void* up, void* out, int32_t B, int32_t n
                int64_t ld_up, int64_t ld_out, hxq_stream_t stream);
 
 /*
+ * ---- tensor-parallel sum after a row-parallel product, decode-sized messages ----
+ * No counterpart in the reference (it has no multi-GPU path); replaces what
+ * torch.distributed.all_reduce (NCCL) would do after o_proj / down_proj.  One kernel per
+ * rank over peer memory: every rank pushes its fp32 partial sums into every rank's receive
+ * buffer with plain peer stores, raises a flag, waits (bounded) for all ranks' flags in its
+ * own buffer and adds the partials from local memory in rank order, rounding once to bf16:
+ * the result is bit-identical on every rank and from run to run.
+ *   peer_buffers[p], peer_flags[p]: HOST arrays of `world` DEVICE pointers, rank p's receive
+ *     buffer (hxq_allreduce_buffer_bytes, 16-byte aligned) and flag array
+ *     (hxq_allreduce_flag_bytes), both zero before the first call and mapped into this
+ *     process (symmetric / IPC memory); the same n_max on every rank, n_max % 8 == 0.
+ *   src: this rank's partial sums, fp32 [n], n <= n_max, n <= 131072; dst: bf16 [n].
+ *   counters: 32 x uint32 of this rank's own device memory, zero before the first call;
+ *     the kernel advances them, so a captured graph can be replayed.
+ *   wait_cycles: limit of the flag wait in SM clock cycles (0 = about one second); on
+ *     expiry *status (device int32, may be NULL) is set to HXQ_E_TIMEOUT and dst is left
+ *     untouched.  Every rank must make the same sequence of calls.
+ */
+size_t hxq_allreduce_buffer_bytes(int32_t world, int64_t n_max);
+size_t hxq_allreduce_flag_bytes(int32_t world);
+int hxq_allreduce_oneshot(void* const* peer_buffers, void* const* peer_flags, int32_t rank, int32_t world,
+                          int64_t n_max, const void* src, void* dst, int64_t n, void* counters,
+                          int64_t wait_cycles, int32_t* status, hxq_stream_t stream);
+
+/*
  * Host helper: CSR row pointer from ascending flat positions
  * (rows = pos / in_features), the derivation HelixLinear does at load
  * (helix_substrate/helix_linear.py:196-203,960-997).  positions, rowptr and
