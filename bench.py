@@ -262,6 +262,8 @@ def main():
     ap.add_argument("--impl", default="hxq_b200")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
+                    help="tensor-parallel sum after down: one-shot peer-memory kernel (default) or NCCL")
     ap.add_argument("--workload", default="gemv", choices=["gemv", "prefill"],
                     help="gemv: the headline decode workload; prefill: tensor-core kernel TFLOP/s (secondary)")
     args = ap.parse_args()
@@ -291,14 +293,37 @@ def main():
     outs = [{k: torch.empty(M, m.out_features, device=dev, dtype=act) for k, m in lay.items()} for lay in layers]
     n_launch_per_step = 3 * L * (-(-M // 4) if M > 4 else 1)
 
+    # tensor-parallel sum after `down`: the one-shot peer-memory kernel, or NCCL if asked for / if
+    # symmetric memory cannot be set up on every rank (the ranks agree on one of the two)
+    oneshot, p32 = None, None
+    if world > 1 and args.allreduce == "p2p" and M <= 16:
+        from helix_substrate_b200.tp import OneShotAllReduce
+        ok = torch.ones(1, device=dev)
+        try:
+            oneshot = OneShotAllReduce(M * HIDDEN, dev)
+        except Exception as e:   # noqa: BLE001 - any set-up failure means "use NCCL", decided together below
+            print(f"[bench rank {rank}] one-shot all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) < 1.0:
+            oneshot = None
+        else:
+            p32 = torch.empty(M, HIDDEN, device=dev, dtype=torch.float32)
+            n_launch_per_step += L
+    allreduce_kind = None if world == 1 else ("p2p-oneshot" if oneshot is not None else "nccl")
+
     def step_kernels():
         """One pass over every linear, straight on the packed weights (C ABI)."""
         for lay, o in zip(layers, outs):
             lay["gate"].packed().matmul(x, out=o["gate"])
             lay["up"].packed().matmul(x, out=o["up"])
-            lay["down"].packed().matmul(xd, out=o["down"])
-            if world > 1:
-                dist.all_reduce(o["down"])
+            if oneshot is not None:
+                lay["down"].packed().matmul(xd, torch.float32, out=p32)
+                oneshot(p32, out=o["down"])
+            else:
+                lay["down"].packed().matmul(xd, out=o["down"])
+                if world > 1:
+                    dist.all_reduce(o["down"])
 
     for _ in range(2):
         step_kernels()
@@ -350,6 +375,10 @@ def main():
     xg, xdd = torch.empty_like(x), torch.empty_like(xd)
     out_h = {k: torch.empty(M, m.out_features, dtype=act).pin_memory() for k, m in layers[-1].items()}
 
+    from helix_substrate_b200.tp import RowParallelHelixLinear
+    down_mods = {id(lay["down"]): (RowParallelHelixLinear(lay["down"], oneshot=oneshot) if world > 1 else lay["down"])
+                 for lay in layers}
+
     def step_e2e():
         xg.copy_(x_h, non_blocking=True)
         xdd.copy_(xd_h, non_blocking=True)
@@ -357,9 +386,7 @@ def main():
         for lay in layers:
             g = lay["gate"](xg)
             u = lay["up"](xg)
-            y = lay["down"](xdd)
-            if world > 1:
-                dist.all_reduce(y)
+            y = down_mods[id(lay["down"])](xdd)
         out_h["gate"].copy_(g, non_blocking=True)
         out_h["up"].copy_(u, non_blocking=True)
         out_h["down"].copy_(y, non_blocking=True)
@@ -413,7 +440,7 @@ def main():
                                "(k=256 codebook, group-128 fp32 affine, two-sided 99.95% sidecar), distinct "
                                f"weights per layer, M={M} bf16 activations",
                    "layers": L, "m": M, "launch": "python" if graph is None else "cuda_graph",
-                   "parallelism": f"tp{world}" if world > 1 else "single",
+                   "parallelism": f"tp{world}" if world > 1 else "single", "allreduce": allreduce_kind,
                    "l2": f"inputs larger than L2 ({nbytes_rank / 1e9:.2f} GB of distinct weights per pass)",
                    "algorithmic_bytes_per_step": nbytes},
         "e2e": {"value": nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,

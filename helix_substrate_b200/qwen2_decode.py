@@ -319,7 +319,7 @@ def main(argv=None):
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--torch-glue", action="store_true", help="run the step's glue in plain torch ops")
-    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--allreduce", default="p2p", choices=["nccl", "p2p"],
                     help="tensor-parallel sum in the fused step: NCCL, or the one-shot peer-memory kernel")
     ap.add_argument("--separate-proj", action="store_true",
                     help="q, k, v and gate, up as separate compressed matrices (7 products per layer instead of 4)")

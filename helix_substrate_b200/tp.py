@@ -89,17 +89,26 @@ def shard_helix_linear(mod: HelixLinear, mode: str, rank: int, world: int) -> He
 
 class RowParallelHelixLinear(nn.Module):
     """Row-parallel shard + the sum over ranks.  ``x`` is this rank's slice of
-    the input features; the result is the full output on every rank."""
+    the input features; the result is the full output on every rank.  With
+    ``oneshot`` (a OneShotAllReduce sized for tokens x out_features) decode-sized
+    calls sum fp32 partials over peer memory; anything larger goes through NCCL."""
 
-    def __init__(self, shard: HelixLinear, group: Optional["torch.distributed.ProcessGroup"] = None):
+    def __init__(self, shard: HelixLinear, group: Optional["torch.distributed.ProcessGroup"] = None,
+                 oneshot: Optional["OneShotAllReduce"] = None):
         super().__init__()
-        self.shard, self.group = shard, group
+        self.shard, self.group, self.oneshot = shard, group, oneshot
         self.in_features, self.out_features = shard.in_features, shard.out_features
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+        if multi and self.oneshot is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            x2 = x.reshape(-1, self.in_features)
+            if x2.shape[0] * self.out_features <= self.oneshot.n_max and x2.shape[0] <= 16:
+                part = self.shard.packed().matmul(x2, torch.float32)
+                return self.oneshot(part).view(*x.shape[:-1], self.out_features)
         y = self.shard(x)
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+        if multi:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
 
