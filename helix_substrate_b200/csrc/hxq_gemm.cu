@@ -8,7 +8,7 @@
 //
 //   warp 0   (1 lane)  TMA: 128x64 index bytes and BN x 64 bf16 activations (128-byte
 //                      swizzle) -> shared memory, completion on an mbarrier
-//   warps 2-9          dequantise the index tile to bf16 in the UMMA K-major
+//   warps 2-17         dequantise the index tile to bf16 in the UMMA K-major
 //                      128B-swizzled layout: lane-replicated codebook lookup, group
 //                      affine in fp32, sidecar deltas folded in (each row's CSR cursor
 //                      walks forward as K advances), proxy fence, arrive
@@ -40,8 +40,14 @@ constexpr int BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzled r
 constexpr int LUT_BYTES = 256 * 128;   // entry c, lane l at byte c*128 + l*4
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int IDX_BYTES = BM * BK;     // 8 KB
-constexpr int NUM_DEQ_WARPS = 8;
+#ifndef HXQ_GEMM_DEQ_WARPS
+#define HXQ_GEMM_DEQ_WARPS 16
+#endif
+constexpr int NUM_DEQ_WARPS = HXQ_GEMM_DEQ_WARPS;          // 8 or 16
+constexpr int ROWS_PER_WARP = BM / NUM_DEQ_WARPS;           // 16 or 8
+constexpr int PASSES = ROWS_PER_WARP / 8;                   // a warp covers 8 rows x 64 columns per pass
 constexpr int NUM_THREADS = 32 * (2 + NUM_DEQ_WARPS);
+static_assert(NUM_DEQ_WARPS == 8 || NUM_DEQ_WARPS == 16, "dequantising warps: 8 or 16");
 
 template <int BN> struct Smem {
     static constexpr int NSUB = BN > 256 ? 2 : 1;     // accumulators (UMMA N <= 256)
@@ -170,17 +176,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------ dequantising warps
-        const int dw = warp - 2;                     // 0..7: rows [16*dw, 16*dw + 16)
-        const int r_a = 16 * dw + (lane >> 2);       // first pass row (local), second pass is r_a + 8
+        const int dw = warp - 2;                     // rows [ROWS_PER_WARP * dw, + ROWS_PER_WARP)
+        const int r_a = ROWS_PER_WARP * dw + (lane >> 2);   // first pass row (local); pass p is r_a + 8 p
         const int jc = lane & 3;                     // 16-column chunk of the 64-column step
         const uint32_t lane4x2 = (uint32_t)lane << 3;
         const bool affine = a.group_size > 0;
-        const int row_a = o0 + r_a, row_b = o0 + r_a + 8;
-        const bool ok_a = row_a < a.out_features, ok_b = row_b < a.out_features;
 
-        auto load_st = [&](int ks, int row, bool okr, float& s, float& t) {
+        auto load_st = [&](int ks, int row, float& s, float& t) {
             s = 1.f; t = 0.f;
-            if (affine && okr) {
+            if (affine && row < a.out_features) {
                 int g = (a.col0 + ks * BK) / a.group_size - a.col0 / a.group_size;
                 g = g < a.n_groups ? g : a.n_groups - 1;
                 const int64_t o = (int64_t)row * a.ld_st + g;
@@ -193,15 +197,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                 }
             }
         };
-        float sa, ta, sb, tb, sa_n, ta_n, sb_n, tb_n;
-        load_st(0, row_a, ok_a, sa_n, ta_n);
-        load_st(0, row_b, ok_b, sb_n, tb_n);
+        float sc_c[PASSES], of_c[PASSES], sc_n[PASSES], of_n[PASSES];
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) load_st(0, o0 + r_a + 8 * p, sc_n[p], of_n[p]);
 
-        // sidecar cursor: lanes 0..15 each follow one of this warp's 16 rows
-        const int row_c = o0 + 16 * dw + lane;
+        // sidecar cursor: lanes 0..ROWS_PER_WARP-1 each follow one of this warp's rows
+        const int row_c = o0 + ROWS_PER_WARP * dw + lane;
         int e_cur = 0, e_end = 0, nc = 0x7fffffff;
         float nd = 0.f;
-        if (a.rowptr != nullptr && lane < 16 && row_c < a.out_features) {
+        if (a.rowptr != nullptr && lane < ROWS_PER_WARP && row_c < a.out_features) {
             e_cur = a.rowptr[row_c];
             e_end = a.rowptr[row_c + 1];
             if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
@@ -210,19 +214,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
         for (int ks = 0; ks < KS; ++ks) {
             const int s = ks % STAGES;
             const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-            sa = sa_n; ta = ta_n; sb = sb_n; tb = tb_n;
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) { sc_c[p] = sc_n[p]; of_c[p] = of_n[p]; }
             if (ks + 1 < KS) {  // next step's scale/offset go out before we block
-                load_st(ks + 1, row_a, ok_a, sa_n, ta_n);
-                load_st(ks + 1, row_b, ok_b, sb_n, tb_n);
+#pragma unroll
+                for (int p = 0; p < PASSES; ++p) load_st(ks + 1, o0 + r_a + 8 * p, sc_n[p], of_n[p]);
             }
             if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
             char* st = stage0 + s * S::STAGE_BYTES;
             const char* idx_s = st + A_BYTES + S::B_BYTES;
 
 #pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
+            for (int pass = 0; pass < PASSES; ++pass) {
                 const int r = r_a + 8 * pass;
-                const float sc = pass ? sb : sa, of = pass ? tb : ta;
+                const float sc = sc_c[pass], of = of_c[pass];
                 const uint4 q = *reinterpret_cast<const uint4*>(idx_s + r * BK + jc * 16);
                 const uint32_t w[4] = {q.x, q.y, q.z, q.w};
                 float v[16];
@@ -245,14 +250,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
 
             // sidecar entries of this warp's rows that fall into this K step
             {
-                const int rr = lane & 15;                       // row (within the warp's 16) this lane follows
+                const int rr = lane & (ROWS_PER_WARP - 1);      // row (within the warp's) this lane follows
                 const int src = 4 * (rr & 7);                   // lane that holds that row's scale/offset
-                const float s0 = __shfl_sync(0xffffffffu, sa, src), t0 = __shfl_sync(0xffffffffu, ta, src);
-                const float s1 = __shfl_sync(0xffffffffu, sb, src), t1 = __shfl_sync(0xffffffffu, tb, src);
-                const float sc = (rr & 8) ? s1 : s0, of = (rr & 8) ? t1 : t0;
+                float sc = __shfl_sync(0xffffffffu, sc_c[0], src), of = __shfl_sync(0xffffffffu, of_c[0], src);
+                if (PASSES > 1) {
+                    const float s1 = __shfl_sync(0xffffffffu, sc_c[PASSES - 1], src);
+                    const float t1 = __shfl_sync(0xffffffffu, of_c[PASSES - 1], src);
+                    if (rr & 8) { sc = s1; of = t1; }
+                }
                 const int k_hi = (ks + 1) * BK;
                 while (nc < k_hi) {                              // nc >= ks*BK: the cursor only moves forward
-                    const int r = 16 * dw + rr;
+                    const int r = ROWS_PER_WARP * dw + rr;
                     const int c = nc - ks * BK;
                     const uint32_t code = (uint8_t)idx_s[r * BK + c];
                     const float wv = fmaf(*reinterpret_cast<const float*>(lut + code * 128 + lane * 4), sc, of) + nd;

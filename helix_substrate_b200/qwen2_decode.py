@@ -361,7 +361,10 @@ def main(argv=None):
                 nxt = run()
             else:
                 pt = torch.tensor([p], device=dev)
-                nxt = model.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
+                if args.torch_glue:
+                    nxt = model.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
+                else:
+                    nxt = model.step_fused(nxt[:, None], pt).argmax(-1)
         e2.record()
         torch.cuda.synchronize()
     ms_dec = e1.elapsed_time(e2) / (args.new - 1)
@@ -376,7 +379,7 @@ def main(argv=None):
             "metric": "decode_tokens_per_s", "value": args.batch * 1000.0 / ms_dec, "unit": "tok/s",
             "ms_per_token_step": ms_dec, "batch": args.batch, "prompt": args.prompt, "new_tokens": args.new,
             "shape": args.shape, "layers": shp.layers, "n_gpus": world, "launch": "python" if run is None else "cuda_graph",
-            "glue": "torch" if (args.torch_glue or run is None) else "fused",
+            "glue": "torch" if args.torch_glue else "fused",
             "projections": "q,k,v,o,gate,up,down" if args.separate_proj else "qkv,o,gate_up,down",
             "allreduce": (args.allreduce if world > 1 else None),
             "hxq_algorithmic_bytes_per_step_per_gpu": hxq_bytes,
