@@ -16,7 +16,7 @@
 //                      tcgen05.commit frees the stage
 //
 // and after the last step warps 2-5 read TMEM (tcgen05.ld), add the bias and store
-// y[m, o].  Three stages (two at BN = 512); every mbarrier wait is bounded and raises a status word.
+// y[m, o].  Two to six stages (as many as fit for the tile width); every mbarrier wait is bounded and raises a status word.
 // The eight dequantising warps pace the kernel (about 800 issue cycles per K step against 525
 // tensor cycles for a 128x256x64 step), so the token tile is made as wide as TMEM allows: at
 // BN = 512 every dequantised tile feeds twice the tensor work.
@@ -52,7 +52,7 @@ static_assert(NUM_DEQ_WARPS == 8 || NUM_DEQ_WARPS == 16, "dequantising warps: 8 
 template <int BN> struct Smem {
     static constexpr int NSUB = BN > 256 ? 2 : 1;     // accumulators (UMMA N <= 256)
     static constexpr int BNS = BN / NSUB;             // tokens per accumulator
-    static constexpr int STAGES = BN > 256 ? 2 : 3;
+    static constexpr int STAGES = BN > 256 ? 2 : (BN == 256 ? 3 : (BN == 128 ? 4 : 6));   // as deep as shared memory allows
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + IDX_BYTES;
     static constexpr int BAR_OFFSET = LUT_BYTES + STAGES * STAGE_BYTES;
@@ -72,6 +72,8 @@ struct GemmArgs {
     int64_t ldy;
     int32_t out_features, in_features, col0, group_size, ld_st, st_dtype, n_groups;
     int32_t M, y_dtype, k_steps;
+    int32_t k_per_split;   // K steps per CTA along gridDim.z (== k_steps when the K range is not split)
+    float* partial;        // [splits][M][out_features] fp32 partial products when split, else nullptr
 };
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -101,7 +103,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
     const int lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BN;     // token tile (fastest: neighbours share the weight tile in L2)
     const int o0 = blockIdx.y * BM;     // output-row tile
-    const int KS = a.k_steps;
+    // this CTA's K steps: [KS0, KS0 + KS) of the whole range
+    const int KS0 = blockIdx.z * a.k_per_split;
+    const int KS = (a.k_steps - KS0 < a.k_per_split) ? a.k_steps - KS0 : a.k_per_split;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -137,10 +141,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                 if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                 char* st = stage0 + s * S::STAGE_BYTES;
                 sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)(IDX_BYTES + S::B_BYTES));
-                sm100::tma_load_2d(st + A_BYTES + S::B_BYTES, &map_idx, &tma_full[s], ks * BK, o0);
+                sm100::tma_load_2d(st + A_BYTES + S::B_BYTES, &map_idx, &tma_full[s], (KS0 + ks) * BK, o0);
 #pragma unroll
                 for (int n = 0; n < S::NSUB; ++n)
-                    sm100::tma_load_2d(st + A_BYTES + n * (S::BNS * BK * 2), &map_x, &tma_full[s], ks * BK, m0 + n * S::BNS);
+                    sm100::tma_load_2d(st + A_BYTES + n * (S::BNS * BK * 2), &map_x, &tma_full[s], (KS0 + ks) * BK, m0 + n * S::BNS);
                 armed = ks + 1;
             }
             if (*abort_flag != 0) {
@@ -185,7 +189,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
         auto load_st = [&](int ks, int row, float& s, float& t) {
             s = 1.f; t = 0.f;
             if (affine && row < a.out_features) {
-                int g = (a.col0 + ks * BK) / a.group_size - a.col0 / a.group_size;
+                int g = (a.col0 + (KS0 + ks) * BK) / a.group_size - a.col0 / a.group_size;
                 g = g < a.n_groups ? g : a.n_groups - 1;
                 const int64_t o = (int64_t)row * a.ld_st + g;
                 if (a.st_dtype == HXQ_F32) {
@@ -208,6 +212,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
         if (a.rowptr != nullptr && lane < ROWS_PER_WARP && row_c < a.out_features) {
             e_cur = a.rowptr[row_c];
             e_end = a.rowptr[row_c + 1];
+            if (KS0 > 0) {   // a later slice of the K range: skip the row's entries in front of it
+                int lo = e_cur, hi = e_end;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (a.cols[mid] < KS0 * BK) lo = mid + 1; else hi = mid;
+                }
+                e_cur = lo;
+            }
             if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
         }
 
@@ -258,10 +270,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                     const float t1 = __shfl_sync(0xffffffffu, of_c[PASSES - 1], src);
                     if (rr & 8) { sc = s1; of = t1; }
                 }
-                const int k_hi = (ks + 1) * BK;
+                const int k_hi = (KS0 + ks + 1) * BK;
                 while (nc < k_hi) {                              // nc >= ks*BK: the cursor only moves forward
                     const int r = ROWS_PER_WARP * dw + rr;
-                    const int c = nc - ks * BK;
+                    const int c = nc - (KS0 + ks) * BK;
                     const uint32_t code = (uint8_t)idx_s[r * BK + c];
                     const float wv = fmaf(*reinterpret_cast<const float*>(lut + code * 128 + lane * 4), sc, of) + nd;
                     *reinterpret_cast<__nv_bfloat16*>(st + r * 128 + ((((c >> 3) ^ (r & 7)) << 4) | ((c & 7) << 1))) =
@@ -280,7 +292,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
             const int quarter = warp & 3;            // TMEM lanes this warp may read: [32*quarter, +32)
             const int row = o0 + 32 * quarter + lane;
             const bool row_ok = row < a.out_features;
-            const float bias = (a.bias != nullptr && row_ok) ? a.bias[row] : 0.f;
+            const float bias = (a.bias != nullptr && row_ok && a.partial == nullptr) ? a.bias[row] : 0.f;
+            float* part = a.partial ? a.partial + (int64_t)blockIdx.z * a.M * a.out_features : nullptr;
             if (sm100::mbar_wait(acc_full, 0u, abort_flag)) {
                 sm100::tc_fence_after_sync();
 #pragma unroll 1
@@ -292,8 +305,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int m = m0 + c0 + j;
-                        if (row_ok && m < a.M)
-                            store_from_f32(a.y, (int64_t)m * a.ldy + row, __uint_as_float(r[j]) + bias, a.y_dtype);
+                        if (row_ok && m < a.M) {
+                            if (part) part[(int64_t)m * a.out_features + row] = __uint_as_float(r[j]);
+                            else store_from_f32(a.y, (int64_t)m * a.ldy + row, __uint_as_float(r[j]) + bias, a.y_dtype);
+                        }
                     }
                 }
             }
@@ -354,6 +369,38 @@ __global__ void __launch_bounds__(256) to_bf16_kernel(const void* x, int x_dtype
     }
 }
 
+// y[m, o] = sum over the K slices of partial[z][m][o], + bias, rounded once (fixed order: deterministic).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int out_features,
+                                                            const float* __restrict__ bias, void* y, int y_dtype, int64_t ldy) {
+    const int64_t total = (int64_t)M * out_features;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / out_features), o = (int)(i - (int64_t)m * out_features);
+        float v = 0.f;
+        for (int z = 0; z < splits; ++z) v += partial[(int64_t)z * total + i];
+        if (bias != nullptr) v += bias[o];
+        store_from_f32(y, (int64_t)m * ldy + o, v, y_dtype);
+    }
+}
+
+// K slices per output tile: enough CTAs to fill the GPU when the tile grid alone does not
+// (one token tile x few row tiles, e.g. down_proj at M <= 64), at least four K steps each.
+static int pick_bn(int M) { return M > 256 ? 512 : (M > 128 ? 256 : (M > 64 ? 128 : 64)); }
+static int sm_count() {
+    int n_sm = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        n_sm <= 0)
+        n_sm = 148;
+    return n_sm;
+}
+static int pick_splits(int grid_m, int grid_o, int k_steps, int n_sm) {
+    const int tiles = grid_m * grid_o;
+    if (tiles * 2 > n_sm) return 1;
+    int s = n_sm / tiles;
+    if (s > 8) s = 8;
+    if (s > k_steps / 4) s = k_steps / 4;
+    return s < 1 ? 1 : s;
+}
+
 bool fast_ok(const hxq_desc* d) {
     return (d->in_features % 16 == 0) && (d->ld_idx % 16 == 0) && aligned_to(d->indices, 16) &&
            (d->col0 % 64 == 0) && (d->group_size == 0 || d->group_size % 64 == 0) && encode_fn() != nullptr;
@@ -361,13 +408,21 @@ bool fast_ok(const hxq_desc* d) {
 
 static int64_t x_pad(const hxq_desc* d) { return ((int64_t)d->in_features + 7) / 8 * 8; }
 
+static size_t xcopy_bytes(const hxq_desc* d, int32_t M) { return (((size_t)M * x_pad(d) * 2 + 255) & ~(size_t)255) + 256; }
+
 size_t workspace_bytes(const hxq_desc* d, int32_t M) {
     if (!fast_ok(d)) return gemv_workspace_bytes(d, 4);
-    return (size_t)M * x_pad(d) * 2 + 256;   // room for a bf16 copy of x when it is not usable in place
+    // room for a bf16 copy of x when it is not usable in place, then the fp32 partials of the K slices
+    // when the output tile grid is too small to fill the GPU
+    size_t split = 0;
+    const int BN = pick_bn(M);
+    const int s = pick_splits((M + BN - 1) / BN, (d->out_features + BM - 1) / BM, (d->in_features + BK - 1) / BK, sm_count());
+    if (s > 1) split = (size_t)s * M * d->out_features * sizeof(float);
+    return xcopy_bytes(d, M) + split;
 }
 
 template <int BN>
-static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const GemmArgs& a, int grid_m, int grid_o,
+static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const GemmArgs& a, int grid_m, int grid_o, int splits,
                   cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -378,7 +433,7 @@ static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const GemmArgs& 
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    gemm_kernel<BN><<<dim3(grid_m, grid_o), NUM_THREADS, Smem<BN>::TOTAL, stream>>>(mi, mx, a);
+    gemm_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, Smem<BN>::TOTAL, stream>>>(mi, mx, a);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
@@ -389,7 +444,7 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
     const bool x_in_place = (x_dtype == HXQ_BF16) && aligned_to(x, 16) && ((ldx * 2) % 16 == 0);
     if (!x_in_place) {
         const int64_t ld = x_pad(d);
-        if (!workspace || ws_bytes < (size_t)M * ld * 2) return HXQ_E_WORKSPACE;
+        if (!workspace || ws_bytes < (size_t)M * ld * 2) return HXQ_E_WORKSPACE;   // (the first xcopy_bytes of the workspace)
         if (!aligned_to(workspace, 16)) return HXQ_E_ALIGN;
         int64_t total = (int64_t)M * ld;
         int blocks = (int)((total + 255) / 256);
@@ -400,7 +455,7 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
         xb = workspace;
         ldxb = ld;
     }
-    const int BN = M > 256 ? 512 : (M > 128 ? 256 : (M > 64 ? 128 : 64));
+    const int BN = pick_bn(M);
     CUtensorMap mi, mx;
     if (!make_map_2d(&mi, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->indices, (uint64_t)d->in_features,
                      (uint64_t)d->out_features, (uint64_t)d->ld_idx, BK, BM, CU_TENSOR_MAP_SWIZZLE_NONE))
@@ -420,10 +475,32 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
     a.k_steps = (d->in_features + BK - 1) / BK;
     const int grid_o = (d->out_features + BM - 1) / BM;
     const int grid_m = (M + BN - 1) / BN;
-    if (BN == 512) return launch<512>(mi, mx, a, grid_m, grid_o, stream);
-    if (BN == 256) return launch<256>(mi, mx, a, grid_m, grid_o, stream);
-    if (BN == 128) return launch<128>(mi, mx, a, grid_m, grid_o, stream);
-    return launch<64>(mi, mx, a, grid_m, grid_o, stream);
+    int splits = 1;
+    a.k_per_split = a.k_steps;
+    a.partial = nullptr;
+    {
+        splits = pick_splits(grid_m, grid_o, a.k_steps, sm_count());
+        const size_t off = xcopy_bytes(d, M);
+        if (splits > 1 && workspace && aligned_to(workspace, 16) &&
+            ws_bytes >= off + (size_t)splits * M * d->out_features * sizeof(float)) {
+            a.k_per_split = (a.k_steps + splits - 1) / splits;
+            splits = (a.k_steps + a.k_per_split - 1) / a.k_per_split;   // no empty slice
+            a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + off);
+        } else {
+            splits = 1;
+        }
+    }
+    int st;
+    if (BN == 512) st = launch<512>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 256) st = launch<256>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 128) st = launch<128>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else st = launch<64>(mi, mx, a, grid_m, grid_o, splits, stream);
+    if (st != HXQ_OK || splits == 1) return st;
+    const int64_t total = (int64_t)M * d->out_features;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
 }  // namespace gemm

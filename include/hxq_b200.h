@@ -148,7 +148,10 @@ int hxq_gemv_static(const hxq_desc* d, const void* x, int x_dtype, int32_t M, in
  * up (the host reads it after synchronising); may be NULL.
  * The workspace of hxq_gemm is plain scratch (a bf16 copy of x when x is not
  * bf16 or not 16-byte aligned): it need not be zeroed and is left dirty, so it
- * must not double as an hxq_gemv workspace.  Shapes the tensor-core kernel does
+ * must not double as an hxq_gemv workspace.  When the output tile grid alone cannot fill
+ * the GPU (one token tile and few row tiles, e.g. down_proj at M = 32) the K range is split over
+ * CTAs and their fp32 partial products, also in the workspace, are added in fixed order by
+ * a second launch; with a workspace too small for them the call runs unsplit.  Shapes the tensor-core kernel does
  * not cover (ragged or unaligned) run through the decode kernels; the call
  * clears the part of the workspace they need first.
  */
