@@ -6,7 +6,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parent / "libhxq_b200.so"
+import os
+
+# HXQ_B200_LIB points at another build of the same library (e.g. one compiled with different tuning macros)
+_LIB_PATH = Path(os.environ.get("HXQ_B200_LIB") or Path(__file__).resolve().parent / "libhxq_b200.so")
 
 HXQ_F32, HXQ_F16, HXQ_BF16 = 0, 1, 2
 

@@ -566,11 +566,11 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
         ring_q0 = (i0 < n_lo ? lo0 + i0 * kUnitBytes : hi0 + (i0 - n_lo) * kUnitBytes) + lane * 16;
         ring_q1 = (i1 < n_lo ? lo0 + i1 * kUnitBytes : hi0 + (i1 - n_lo) * kUnitBytes) + lane * 16;
         const uint32_t n_hi = n_q > n_lo ? n_q - n_lo : 0u;
-        // token m at + m * 32 * xs_lane; a lane's 16-byte pieces 512 bytes apart (conflict-free) unless
-        // a bulk copy lays the chunk down contiguously
-        ring_x = hi0 + n_hi * kUnitBytes + warp * (MP * 32 * xs_lane) + lane * (HXQ_GEMV_TMA ? xs_lane : 16);
+        // token m at + m * 32 * xs_lane; a lane's 32 or 64 bytes are contiguous (spreading its 16-byte pieces
+        // 512 bytes apart removes the 2-way bank conflict of the read-back and measured 2.8 us SLOWER on down_proj)
+        ring_x = hi0 + n_hi * kUnitBytes + warp * (MP * 32 * xs_lane) + lane * xs_lane;
     }
-    constexpr int kXPiece = HXQ_GEMV_TMA ? 16 : 512;   // distance between a lane's consecutive 16-byte pieces
+    constexpr int kXPiece = 16;   // distance between a lane's consecutive 16-byte pieces
 #if HXQ_GEMV_TMA
     // one mbarrier per unit buffer, at the end of the slot area; only this warp ever touches its two
     const uint32_t bar0 = lut_base + kLutBytes + (uint32_t)a.slot_bytes - kLeanBarBytes + warp * 16;
