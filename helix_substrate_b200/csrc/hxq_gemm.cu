@@ -393,8 +393,10 @@ static int sm_count() {
     return n_sm;
 }
 static int pick_splits(int grid_m, int grid_o, int k_steps, int n_sm) {
+    // only with a single token tile: with more, the fp32 partials (splits x M x OUT) cost more traffic than
+    // the idle SMs are worth (measured: k/v at M = 2048 / 8192 split 8 / 2 ways lost 5-10 % of the whole pass)
     const int tiles = grid_m * grid_o;
-    if (tiles * 2 > n_sm) return 1;
+    if (grid_m > 1 || tiles * 2 > n_sm) return 1;
     int s = n_sm / tiles;
     if (s > 8) s = 8;
     if (s > k_steps / 4) s = k_steps / 4;
