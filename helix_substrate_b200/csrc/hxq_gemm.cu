@@ -15,7 +15,7 @@
 //   warp 1   (1 lane)  4 x tcgen05.mma (K = 16 each) accumulating fp32 in TMEM;
 //                      tcgen05.commit frees the stage
 //
-// and after the last step warps 2-5 read TMEM (tcgen05.ld), add the bias and store
+// and after the last step the dequantising warps read TMEM (tcgen05.ld), add the bias and store
 // y[m, o].  Two to six stages (as many as fit for the tile width); every mbarrier wait is bounded and raises a status word.
 // The eight dequantising warps pace the kernel (about 800 issue cycles per K step against 525
 // tensor cycles for a 128x256x64 step), so the token tile is made as wide as TMEM allows: at
@@ -287,27 +287,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
             if (lane == 0) sm100::mbar_arrive(&a_full[s]);
         }
 
-        // ------------------------------------------------------------ epilogue (warps 2..5)
-        if (warp < 6) {
-            const int quarter = warp & 3;            // TMEM lanes this warp may read: [32*quarter, +32)
+        // ------------------------------------------------------------ epilogue (all dequantising warps)
+        // A warp may read the 32 TMEM lanes of its quarter (warp % 4) only: the warps of one quarter share
+        // its 32 output rows and split the token columns between them.
+        {
+            constexpr int COL_GROUPS = (BN / 32 < NUM_DEQ_WARPS / 4) ? BN / 32 : NUM_DEQ_WARPS / 4;
+            constexpr int COLS_PER_GROUP = BN / COL_GROUPS;
+            const int quarter = warp & 3;
+            const int cg = dw >> 2;
             const int row = o0 + 32 * quarter + lane;
             const bool row_ok = row < a.out_features;
-            const float bias = (a.bias != nullptr && row_ok && a.partial == nullptr) ? a.bias[row] : 0.f;
-            float* part = a.partial ? a.partial + (int64_t)blockIdx.z * a.M * a.out_features : nullptr;
-            if (sm100::mbar_wait(acc_full, 0u, abort_flag)) {
+            if (cg < COL_GROUPS && sm100::mbar_wait(acc_full, 0u, abort_flag)) {
                 sm100::tc_fence_after_sync();
+                float* part = a.partial ? a.partial + (int64_t)blockIdx.z * a.M * a.out_features : nullptr;
+                const float bias = (a.bias != nullptr && row_ok && part == nullptr) ? a.bias[row] : 0.f;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = cg * COLS_PER_GROUP; c0 < (cg + 1) * COLS_PER_GROUP; c0 += 32) {
                     if (m0 + c0 >= a.M) break;       // warp-uniform
                     uint32_t r[32];
                     sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0, r);
                     sm100::tmem_ld_wait();
+                    if (part != nullptr) {           // warp-uniform: fp32 partial of this K slice
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int m = m0 + c0 + j;
-                        if (row_ok && m < a.M) {
-                            if (part) part[(int64_t)m * a.out_features + row] = __uint_as_float(r[j]);
-                            else store_from_f32(a.y, (int64_t)m * a.ldy + row, __uint_as_float(r[j]) + bias, a.y_dtype);
+                        for (int j = 0; j < 32; ++j) {
+                            const int m = m0 + c0 + j;
+                            if (row_ok && m < a.M) part[(int64_t)m * a.out_features + row] = __uint_as_float(r[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int m = m0 + c0 + j;
+                            if (row_ok && m < a.M)
+                                store_from_f32(a.y, (int64_t)m * a.ldy + row, __uint_as_float(r[j]) + bias, a.y_dtype);
                         }
                     }
                 }
