@@ -1,10 +1,9 @@
 #!/usr/bin/env python3
 """Generate the golden vectors under tests/golden/ from the REFERENCE itself.
 
-Run once, in a container that has the reference checkout (default
-/root/reference, override with HXQ_REFERENCE_DIR):
+Run once, on a machine that has a checkout of the reference:
 
-    python tests/golden/make_golden.py
+    HXQ_REFERENCE_DIR=<reference checkout> python tests/golden/make_golden.py
 
 The reference package does not import as shipped (its modules were renamed
 cdna* -> hxq* without updating the imports), so this script builds a throw-away
@@ -27,7 +26,9 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("HXQ_REFERENCE_DIR", "/root/reference"))
+if "HXQ_REFERENCE_DIR" not in os.environ:
+    raise SystemExit("set HXQ_REFERENCE_DIR to a checkout of echo313unfolding/helix-substrate")
+REF = Path(os.environ["HXQ_REFERENCE_DIR"])
 
 _ALIASES = {
     "cdna_encoder.py": "hxq_encoder.py",
