@@ -1077,6 +1077,7 @@ static int lean_max_warps(const GemvPlan& p, int MP, int x_dtype) {
 // The index matrix as a 2-D tensor of 32-bit words for the bulk tensor copies (a box is at most
 // 256 elements wide: 128 words are the 512 index bytes of one chunk), 8 rows per box.  The
 // encoder is a driver entry point, looked up once.
+#if HXQ_GEMV_TMA
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1091,6 +1092,7 @@ static EncodeTiledFn gemv_encode_fn() {
     }
     return fn;
 }
+#endif
 static bool gemv_index_map(CUtensorMap* map, const hxq_desc* d) {
 #if HXQ_GEMV_TMA
     EncodeTiledFn fn = gemv_encode_fn();

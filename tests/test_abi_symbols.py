@@ -57,3 +57,19 @@ def test_csr_helper():
     bad = np.array([5, 5], dtype=np.int64)
     assert L.hxq_csr_from_positions(bad.ctypes.data, 2, 64, 32, rp.ctypes.data, cols.ctypes.data) == _lib.HXQ_E_ARG
     assert L.hxq_csr_from_positions(None, 0, 64, 32, rp.ctypes.data, None) == 0 and rp[64] == 0
+
+
+def test_glue_and_allreduce_entry_points_validate_without_a_device():
+    from helix_substrate_b200 import _lib
+    L = _lib.lib()
+    assert L.hxq_add_rmsnorm(None, None, None, None, 1, 64, 64, 64, 64, 1e-6, None) == _lib.HXQ_E_ARG
+    assert L.hxq_rope_append(None, 0, None, None, None, None, 0, None, None, 1, 4, 2, 64, 16, None) == _lib.HXQ_E_ARG
+    assert L.hxq_swiglu(None, None, None, 1, 64, 64, 64, 64, None) == _lib.HXQ_E_ARG
+    assert L.hxq_attn_decode(None, 0, None, None, None, None, 0, None, 0, 1, 4, 2, 64, 16, 0.125, None) == _lib.HXQ_E_ARG
+    # sizes: 4-byte partial + 2 floats per (sequence, head, 64-row chunk); 2 slots x world x n_max floats
+    assert L.hxq_attn_decode_workspace_bytes(2, 28, 128, 2184) == 2 * 28 * 35 * 130 * 4
+    assert L.hxq_allreduce_buffer_bytes(4, 3584) == 2 * 4 * 3584 * 4
+    assert L.hxq_allreduce_flag_bytes(8) == 2 * 8 * 32 * 4
+    assert L.hxq_allreduce_buffer_bytes(9, 3584) == 0 and L.hxq_allreduce_buffer_bytes(2, 0) == 0
+    assert L.hxq_allreduce_oneshot(None, None, 0, 2, 64, None, None, 64, None, 0, None, None) == _lib.HXQ_E_ARG
+
