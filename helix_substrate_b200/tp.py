@@ -124,7 +124,10 @@ class OneShotAllReduce:
     writing their partials and flags into this rank's buffer before the call."""
 
     def __init__(self, n_max: int, device, group=None, wait_ms: float = 1000.0):
+        import os
         import torch.distributed as dist
+        # plain peer mappings are all the kernel uses: do not bind the buffer to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         from . import _lib
         group = group if group is not None else dist.group.WORLD
