@@ -13,7 +13,7 @@ import helix_substrate_b200 as _impl
 __version__ = _impl.__version__
 
 _SUBMODULES = (
-    "helix_linear", "helix_affine_linear", "triton_vq_matmul", "triton_affine_group_matmul",
+    "helix_linear", "helix_affine_linear", "triton_vq_matmul", "triton_affine_group_matmul", "triton_affine_matmul",
     "cdnav3_reader", "cdnav3_writer", "hxq_reader_v3", "hxq_writer_v3", "generate_sidecars_v3",
     "tensor_policy", "hf_quantizer", "hf_integration", "hxq_writer_gpu", "tp", "packed",
 )

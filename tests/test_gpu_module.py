@@ -194,3 +194,22 @@ def test_block_affine_module_vs_reference():
     idx, sc, bab, stats = quantize_linear_to_affine(t("weight").to(DEV), 256)
     assert torch.equal(idx.cpu(), t("indices")) and torch.equal(sc.cpu(), t("scales"))
     assert torch.equal(bab.cpu(), t("biases_ab")) and stats["cosine"] > 0.999
+
+
+@pytest.mark.parametrize("n_out,n_in,M", [(264, 1024, 1), (96, 592, 4), (128, 2048, 40)])
+def test_per_tensor_affine_operator(n_out, n_in, M):
+    """fused_affine_matmul (reference: helix_substrate/triton_affine_matmul.py:110-167): the byte ramp
+    k * step + offset as the codebook of the ordinary kernels."""
+    from helix_substrate_b200.triton_affine_matmul import fused_affine_matmul, affine_matmul_reference
+    gen = torch.Generator(device=DEV).manual_seed(n_in + M)
+    idx = torch.randint(0, 256, (n_out, n_in), dtype=torch.uint8, device=DEV, generator=gen)
+    x = torch.randn(M, n_in, device=DEV, generator=gen)
+    bias = torch.randn(n_out, device=DEV, generator=gen)
+    step, offset = 0.00037, -0.047
+    y = fused_affine_matmul(x, idx, step, offset, bias)
+    assert y.dtype == torch.float32 and y.shape == (M, n_out)
+    ref = x.double() @ (idx.double() * step + offset).t() + bias.double()
+    tol = 1e-3 if M <= 16 else 1e-2          # fp32 decode kernels / bf16 tensor-core kernel
+    assert rel_l2(y.double().cpu().numpy(), ref.cpu().numpy()) < tol
+    assert rel_l2(affine_matmul_reference(x, idx, step, offset, bias).double().cpu().numpy(), ref.cpu().numpy()) < 1e-4
+

@@ -29,6 +29,7 @@ def test_drop_in_package_names():
     from helix_substrate.helix_linear import HelixLinear, load_cdna_factors, swap_to_helix  # noqa: F401
     from helix_substrate.triton_vq_matmul import fused_vq_matmul, get_kernel_metadata  # noqa: F401
     from helix_substrate.triton_affine_group_matmul import fused_affine_group_matmul  # noqa: F401
+    from helix_substrate.triton_affine_matmul import fused_affine_matmul, affine_matmul_reference  # noqa: F401
     from helix_substrate.hf_integration import HelixQuantizationConfig
     assert R2 is CDNAv3Reader and W2 is CDNAv3Writer
     assert helix_substrate.HelixLinear is HelixLinear
@@ -187,3 +188,22 @@ def test_hf_round_trip_builds_shells_and_keeps_rope(tmp_path):
     assert n == 14 and isinstance(loaded.lm_head, nn.Linear)
     assert torch.equal(loaded.model.embed_tokens.weight, model.model.embed_tokens.weight)
     assert torch.allclose(loaded.model.rotary_emb.inv_freq, inv_ref)
+
+
+def test_per_tensor_affine_reference_formula_on_cpu():
+    """affine_matmul_reference (any device) is the dense product with W = idx * step + offset."""
+    import numpy as np
+    import torch
+    from helix_substrate.triton_affine_matmul import affine_matmul_reference, fused_affine_matmul
+    rng = np.random.default_rng(5)
+    idx = torch.from_numpy(rng.integers(0, 256, (24, 80), dtype=np.uint8))
+    x = torch.from_numpy(rng.standard_normal((3, 80)).astype(np.float32))
+    b = torch.from_numpy(rng.standard_normal(24).astype(np.float32))
+    y = affine_matmul_reference(x, idx, 0.0125, -1.5, b)
+    w = idx.double() * 0.0125 - 1.5
+    ref = x.double() @ w.t() + b.double()
+    assert torch.allclose(y.double(), ref, rtol=1e-4, atol=1e-4)
+    import pytest
+    with pytest.raises(AssertionError):      # the fused operator is CUDA only, like the reference's
+        fused_affine_matmul(x, idx, 0.0125, -1.5)
+
