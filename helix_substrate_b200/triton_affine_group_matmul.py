@@ -44,8 +44,38 @@ def fused_affine_group_matmul(x: torch.Tensor, indices: torch.Tensor, scales: to
     return _weight(indices, scales, offsets, group_size, bias).matmul(x, out_dtype=torch.float32)
 
 
-def fused_affine_group_matmul_packed6(*args, **kwargs):
-    raise NotImplementedError("6-bit packed indices (k=64) are a different codec, outside this path")
+def unpack6(packed: torch.Tensor, out_features: int, in_features: int) -> torch.Tensor:
+    """6-bit indices, four values in three bytes (b0 | b1 << 8 | b2 << 16 holds v0..v3 from the low
+    bits up, helix_substrate/triton_affine_group_matmul.py:234-238), to one byte per value
+    [out_features, in_features].  Plain torch ops, any device."""
+    assert packed.dtype == torch.uint8 and in_features % 4 == 0
+    assert packed.numel() == out_features * in_features * 3 // 4, "packed size does not match OUT x IN x 3/4"
+    b = packed.reshape(out_features, in_features // 4, 3).to(torch.int32)
+    w = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16)
+    v = torch.stack([(w >> (6 * k)) & 0x3F for k in range(4)], dim=-1)
+    return v.reshape(out_features, in_features).to(torch.uint8)
+
+
+def pack6(indices: torch.Tensor) -> torch.Tensor:
+    """Inverse of unpack6 for values < 64 (flat uint8 of OUT * IN * 3 / 4 bytes)."""
+    assert indices.dtype == torch.uint8 and indices.ndim == 2 and indices.shape[1] % 4 == 0
+    assert int(indices.max()) < 64 if indices.numel() else True
+    v = indices.reshape(indices.shape[0], -1, 4).to(torch.int32)
+    w = v[..., 0] | (v[..., 1] << 6) | (v[..., 2] << 12) | (v[..., 3] << 18)
+    return torch.stack([w & 0xFF, (w >> 8) & 0xFF, (w >> 16) & 0xFF], dim=-1).to(torch.uint8).reshape(-1)
+
+
+def fused_affine_group_matmul_packed6(x: torch.Tensor, packed_indices: torch.Tensor, scales: torch.Tensor,
+                                      offsets: torch.Tensor, out_features: int, in_features: int,
+                                      group_size: int = 128, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """The reference's 6-bit variant (helix_substrate/triton_affine_group_matmul.py:256-298), any N:
+    the packed bytes are expanded to one byte per index on the device (torch ops, every call: a
+    caller that decodes repeatedly should keep ``unpack6``'s result and use fused_affine_group_matmul)
+    and the product runs on the ordinary kernels."""
+    assert x.is_cuda and packed_indices.is_cuda
+    assert x.ndim == 2 and x.shape[1] == in_features
+    idx = unpack6(packed_indices, out_features, in_features)
+    return fused_affine_group_matmul(x, idx, scales, offsets, group_size=group_size, bias=bias)
 
 
 def affine_group_matmul_reference(x: torch.Tensor, indices: torch.Tensor, scales: torch.Tensor,

@@ -213,3 +213,20 @@ def test_per_tensor_affine_operator(n_out, n_in, M):
     assert rel_l2(y.double().cpu().numpy(), ref.cpu().numpy()) < tol
     assert rel_l2(affine_matmul_reference(x, idx, step, offset, bias).double().cpu().numpy(), ref.cpu().numpy()) < 1e-4
 
+
+@pytest.mark.parametrize("M", [1, 3])
+def test_six_bit_packed_affine_group_operator(M):
+    """fused_affine_group_matmul_packed6 (reference: N = 1 only) against the unpacked product."""
+    from helix_substrate_b200.triton_affine_group_matmul import (
+        fused_affine_group_matmul, fused_affine_group_matmul_packed6, pack6)
+    n_out, n_in, G = 72, 512, 128
+    gen = torch.Generator(device=DEV).manual_seed(M)
+    idx = torch.randint(0, 64, (n_out, n_in), dtype=torch.uint8, device=DEV, generator=gen)
+    s = (0.01 + 0.001 * torch.rand(n_out, n_in // G, device=DEV, generator=gen)).half()
+    t = (0.02 * torch.randn(n_out, n_in // G, device=DEV, generator=gen)).half()
+    x = torch.randn(M, n_in, device=DEV, generator=gen)
+    y = fused_affine_group_matmul_packed6(x, pack6(idx), s, t, n_out, n_in, G)
+    assert torch.equal(y, fused_affine_group_matmul(x, idx, s, t, G))
+    w = idx.double() * s.double().repeat_interleave(G, 1) + t.double().repeat_interleave(G, 1)
+    assert rel_l2(y.double().cpu().numpy(), (x.double() @ w.t()).cpu().numpy()) < 1e-3
+

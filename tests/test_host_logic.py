@@ -207,3 +207,20 @@ def test_per_tensor_affine_reference_formula_on_cpu():
     with pytest.raises(AssertionError):      # the fused operator is CUDA only, like the reference's
         fused_affine_matmul(x, idx, 0.0125, -1.5)
 
+
+def test_six_bit_packing_round_trip_and_bit_layout():
+    """unpack6 follows the reference kernel's formulas (v0 = b0 & 63, v1 = (b0 >> 6 | b1 << 2) & 63,
+    v2 = (b1 >> 4 | b2 << 4) & 63, v3 = b2 >> 2)."""
+    import numpy as np
+    import torch
+    from helix_substrate.triton_affine_group_matmul import pack6, unpack6
+    rng = np.random.default_rng(9)
+    idx = torch.from_numpy(rng.integers(0, 64, (7, 24), dtype=np.uint8))
+    packed = pack6(idx)
+    assert packed.dtype == torch.uint8 and packed.numel() == 7 * 24 * 3 // 4
+    assert torch.equal(unpack6(packed, 7, 24), idx)
+    b = packed.reshape(7, 6, 3).numpy().astype(np.int64)
+    b0, b1, b2 = b[..., 0], b[..., 1], b[..., 2]
+    ref = np.stack([b0 & 63, ((b0 >> 6) | (b1 << 2)) & 63, ((b1 >> 4) | (b2 << 4)) & 63, (b2 >> 2) & 63], -1)
+    assert np.array_equal(ref.reshape(7, 24), idx.numpy())
+
