@@ -73,3 +73,22 @@ def test_glue_and_allreduce_entry_points_validate_without_a_device():
     assert L.hxq_allreduce_buffer_bytes(9, 3584) == 0 and L.hxq_allreduce_buffer_bytes(2, 0) == 0
     assert L.hxq_allreduce_oneshot(None, None, 0, 2, 64, None, None, 64, None, 0, None, None) == _lib.HXQ_E_ARG
 
+
+def test_static_scratch_covers_every_qwen25_projection():
+    """The header promises that hxq_gemv_static's 2 MiB array is enough for every Qwen2.5-7B / 14B
+    projection (also the fused qkv / gate_up ones) at M <= 16: check the sizing function, which
+    needs no device (it falls back to 148 SMs)."""
+    from helix_substrate_b200 import _lib
+    L = _lib.lib()
+    dummy = np.zeros(64, dtype=np.uint8)          # never dereferenced by the sizing call
+    shapes = [(3584, 3584), (512, 3584), (4608, 3584), (18944, 3584), (37888, 3584), (3584, 18944),
+              (5120, 5120), (1024, 5120), (7168, 5120), (13824, 5120), (27648, 5120), (5120, 13824)]
+    for n_out, n_in in shapes:
+        d = _lib.HxqDesc()
+        d.out_features, d.in_features, d.group_size, d.ld_idx = n_out, n_in, 128, n_in
+        d.indices = d.codebook = d.scales = d.offsets = dummy.ctypes.data
+        d.st_dtype, d.ld_st = _lib.HXQ_F32, n_in // 128
+        for M in (1, 2, 4, 16):
+            nb = L.hxq_gemv_workspace_bytes(C.byref(d), M)
+            assert 0 < nb <= (2 << 20), (n_out, n_in, M, nb)
+
