@@ -13,7 +13,7 @@ there.  Nothing here is needed at test time: tests read only the .npz files.
 Each case records the seeded inputs together with what the reference's own
 CPU code returned for them (CDNAv3Reader.reconstruct, HelixLinear forward /
 _dequant_tile / decode_weight, affine_group_matmul_reference,
-HelixAffineLinear, the writer's k-means / assignment / outlier selection).
+HelixAffineLinear, affine_matmul_reference, the writer's k-means / assignment / outlier selection).
 """
 
 from __future__ import annotations
@@ -214,6 +214,18 @@ def main():
         "data": data, "centroids": cents.astype(np.float32), "assignments": assign,
         "chunked_assign": idx_full, "outlier_tensor": t2, "outlier_positions": pos,
         "outlier_values": vals,
+    }
+
+    # I. per-tensor affine operator, CPU statement (triton_affine_matmul.py:170-187)
+    from helix_substrate.triton_affine_matmul import affine_matmul_reference
+    rs = np.random.RandomState(13)
+    idx = torch.from_numpy(rs.randint(0, 256, size=(80, 592)).astype(np.uint8))
+    xx = torch.from_numpy(rs.randn(3, 592).astype(np.float32))
+    b = torch.from_numpy(rs.randn(80).astype(np.float32))
+    step, offset = 0.00037, -0.047
+    out["per_tensor_affine_80x592"] = {
+        "indices": idx.numpy(), "x": xx.numpy(), "bias": b.numpy(), "step": np.asarray(step),
+        "offset": np.asarray(offset), "y": affine_matmul_reference(xx, idx, step, offset, b).numpy(),
     }
 
     for name, rec in out.items():

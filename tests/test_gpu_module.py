@@ -230,3 +230,11 @@ def test_six_bit_packed_affine_group_operator(M):
     w = idx.double() * s.double().repeat_interleave(G, 1) + t.double().repeat_interleave(G, 1)
     assert rel_l2(y.double().cpu().numpy(), (x.double() @ w.t()).cpu().numpy()) < 1e-3
 
+
+def test_per_tensor_affine_operator_vs_reference_golden():
+    from helix_substrate_b200.triton_affine_matmul import fused_affine_matmul
+    g = load_golden("per_tensor_affine_80x592")
+    t = lambda a: torch.from_numpy(a).to(DEV)
+    y = fused_affine_matmul(t(g["x"]), t(g["indices"]), float(g["step"]), float(g["offset"]), t(g["bias"]))
+    assert rel_l2(y.cpu().numpy(), g["y"]) < 1e-3
+

@@ -129,3 +129,16 @@ def test_group_affine_fit_is_least_squares():
     for ds, dt in ((1e-3, 0), (0, 1e-3), (-1e-3, 1e-3)):
         worse = ((w - O.gather_affine(cb, idx, s + ds, t + dt, 128)) ** 2).sum()
         assert worse >= fit * (1 - 1e-6)
+
+
+def test_per_tensor_affine_statement_matches_the_reference(golden):
+    """The torch restatement of affine_matmul_reference against what the reference's own returned."""
+    import torch
+    from helix_substrate_b200.triton_affine_matmul import affine_matmul_reference
+    g = golden("per_tensor_affine_80x592")
+    y = affine_matmul_reference(torch.from_numpy(g["x"]), torch.from_numpy(g["indices"]), float(g["step"]),
+                                float(g["offset"]), torch.from_numpy(g["bias"]))
+    assert np.allclose(y.numpy(), g["y"], rtol=1e-5, atol=1e-5)
+    w = g["indices"].astype(np.float64) * float(g["step"]) + float(g["offset"])
+    assert np.allclose(g["x"].astype(np.float64) @ w.T + g["bias"], g["y"], rtol=1e-4, atol=1e-4)
+
