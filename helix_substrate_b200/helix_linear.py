@@ -126,7 +126,8 @@ class HelixLinear(nn.Module):
         if self.sidecar_positions is not None and self.sidecar_values is not None:
             pos = self.sidecar_positions.long()
             rows, cols = pos // n_in, pos % n_in
-            vq = self.codebook[self.indices.reshape(-1).long()[pos]]
+            # gather the nnz index bytes first, widen only those (never the whole matrix)
+            vq = self.codebook[self.indices.reshape(-1)[pos].long()]
             if self.group_scales is not None:
                 g = (self.col0 + cols) // self.group_size - self.col0 // self.group_size
                 vq = (vq * self.group_scales.float()[rows, g]) + self.group_offsets.float()[rows, g]

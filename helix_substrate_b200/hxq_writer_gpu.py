@@ -23,14 +23,32 @@ import torch
 _KMEANS_MAX_SAMPLES = 500_000
 
 
+_subsample_cache: dict = {}
+
+
+def _subsample_positions(n: int) -> torch.Tensor:
+    """The reference writer's subsample: RandomState(42).choice(n, 500 000, replace=False)
+    (helix_substrate/hxq_writer_v3.py:422-437).  It depends on n alone, so it is drawn once
+    per tensor size (a full permutation of n on the host) and kept."""
+    pos = _subsample_cache.get(n)
+    if pos is None:
+        import numpy as np
+        pos = torch.from_numpy(np.random.RandomState(42).choice(n, _KMEANS_MAX_SAMPLES, replace=False).astype("int64"))
+        if len(_subsample_cache) < 16:
+            _subsample_cache[n] = pos
+    return pos
+
+
 def kmeans_codebook(flat: torch.Tensor, n_clusters: int = 256, max_iters: int = 10,
                     rtol: float = 1e-3) -> torch.Tensor:
-    """1-D Lloyd on a RandomState(42)-style subsample with percentile
-    initialisation and the reference's relative-movement stop."""
+    """1-D Lloyd on the reference's RandomState(42) subsample with percentile
+    initialisation and the reference's relative-movement stop.  Same samples and the same
+    iteration as the reference's CPU k-means; centroids can differ from it in the last bits
+    (fp32 sums in another order), so a codebook made here is not bit-identical to one the
+    reference writer makes - indices are always the nearest entry of whichever codebook is given."""
     n = flat.numel()
     if n > _KMEANS_MAX_SAMPLES:
-        g = torch.Generator(device=flat.device).manual_seed(42)
-        sample = flat[torch.randint(0, n, (_KMEANS_MAX_SAMPLES,), device=flat.device, generator=g)]
+        sample = flat[_subsample_positions(n).to(flat.device)]
     else:
         sample = flat
     sample = sample.float().sort().values
@@ -55,8 +73,14 @@ def kmeans_codebook(flat: torch.Tensor, n_clusters: int = 256, max_iters: int = 
 
 def assign_indices(flat: torch.Tensor, codebook: torch.Tensor) -> torch.Tensor:
     """Nearest entry of a sorted codebook, uint8."""
-    mids = (codebook[1:] + codebook[:-1]) * 0.5
-    return torch.bucketize(flat.float().contiguous(), mids.contiguous(), right=False).to(torch.uint8)
+    cb = codebook.double()
+    mids = ((cb[1:] + cb[:-1]) * 0.5).contiguous()     # exact in fp64: a rounded fp32 midpoint misplaces values next to it
+    out = torch.empty(flat.numel(), dtype=torch.uint8, device=flat.device)
+    step = 1 << 24                                      # bounded fp64 temporaries
+    src = flat.reshape(-1)
+    for a in range(0, src.numel(), step):
+        out[a:a + step] = torch.bucketize(src[a:a + step].double(), mids, right=False).to(torch.uint8)
+    return out.view(flat.shape)
 
 
 def find_outliers_percentile(weight: torch.Tensor, percentile: float):

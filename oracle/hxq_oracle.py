@@ -281,6 +281,17 @@ def chunked_assign(flat, codebook, chunk=1 << 18):
     return out
 
 
+def assign_sorted(flat, codebook):
+    """chunked_assign for a strictly increasing codebook in one pass: the nearest entry
+    is found by bisecting the midpoints between neighbours (ties go to the lower index,
+    as argmin's first minimum does).  Used where the 256-way distance table of
+    chunked_assign is too slow (16 M-element tensors); the tests check both agree."""
+    flat = np.asarray(flat, dtype=F32)
+    cb = np.asarray(codebook, dtype=F32)
+    mids = ((cb[1:].astype(np.float64) + cb[:-1].astype(np.float64)) * 0.5)
+    return np.searchsorted(mids, flat.astype(np.float64), side="left").astype(np.uint8)
+
+
 def kmeans_codebook(flat, n_clusters=256, max_samples=500_000):
     """Codebook fitted on a RandomState(42) subsample of at most 500 k values
     (hxq_writer_v3.py:422-437)."""

@@ -3,7 +3,7 @@
 
 Run once, on a machine that has a checkout of the reference:
 
-    HXQ_REFERENCE_DIR=<reference checkout> python tests/golden/make_golden.py
+    HXQ_REFERENCE_DIR=<reference checkout> python tests/golden/make_golden.py [case ...]
 
 The reference package does not import as shipped (its modules were renamed
 cdna* -> hxq* without updating the imports), so this script builds a throw-away
@@ -74,6 +74,7 @@ def main():
 
     torch.set_num_threads(1)
     out = {}
+    only = set(sys.argv[1:]) or None   # optional list of case names: write only those files
 
     def cdna_case(tag, tensor, policy, x, bias=None, block=(0, 0)):
         with tempfile.TemporaryDirectory() as tmp:
@@ -228,7 +229,33 @@ def main():
         "offset": np.asarray(offset), "y": affine_matmul_reference(xx, idx, step, offset, b).numpy(),
     }
 
+    # J. The 4096 x 4096 single-linear benchmark configuration, exactly as stated: Student-t(5)
+    #    seed 0 at std 0.02, reference writer (k-means k=256, two-sided 99.95 % uncapped sidecar,
+    #    no affine), x[1, 4096] fp32 ~ N(0,1).  The 16 MB index matrix is not stored: its SHA-256,
+    #    per-row sums of the reconstruction, a few full rows and the forward output pin it.
+    if only is None or "config1_4096x4096" in only:
+        import hashlib
+        t = _student_t((4096, 4096), seed=0)
+        pol = TensorPolicy(tensor_class=TensorClass.FFN, storage_mode="codebook+sidecar",
+                           n_clusters=256, use_kmeans=True, sidecar_enabled=True,
+                           percentile=99.95, max_corrections=0)
+        x = np.random.default_rng(1).standard_normal((1, 4096)).astype(np.float32)
+        full = cdna_case("config1", t, pol, x)
+        rows = np.asarray([0, 1, 7, 255, 256, 1023, 2048, 4095], dtype=np.int64)
+        out["config1_4096x4096"] = {
+            "codebook": full["codebook"], "x": x, "y_forward": full["y_forward"], "y_naive": full["y_naive"],
+            "indices_sha256": np.frombuffer(hashlib.sha256(np.ascontiguousarray(full["indices"]).tobytes()).digest(),
+                                            dtype=np.uint8).copy(),
+            "sidecar_positions": full["sidecar_positions"], "sidecar_values": full["sidecar_values"],
+            "rows": rows, "reconstruct_rows": full["reconstruct"][rows],
+            "reconstruct_row_sums_f64": full["reconstruct"].astype(np.float64).sum(1),
+            "weight_sha256": np.frombuffer(hashlib.sha256(t.tobytes()).digest(), dtype=np.uint8).copy(),
+            "memory_savings": full["memory_savings"],
+        }
+
     for name, rec in out.items():
+        if only is not None and name not in only:
+            continue
         path = HERE / f"{name}.npz"
         np.savez_compressed(path, **rec)
         print(f"{name}: {path.stat().st_size / 1024:.1f} KiB")

@@ -142,3 +142,39 @@ def test_per_tensor_affine_statement_matches_the_reference(golden):
     w = g["indices"].astype(np.float64) * float(g["step"]) + float(g["offset"])
     assert np.allclose(g["x"].astype(np.float64) @ w.T + g["bias"], g["y"], rtol=1e-4, atol=1e-4)
 
+
+
+# --------------------------------------------------------------------------- the 4096 x 4096 benchmark configuration
+
+def _config1_weight():
+    rng = np.random.default_rng(0)
+    w = rng.standard_t(5, size=(4096, 4096)).astype(np.float32)
+    w *= np.float32(0.02) / w.std()
+    return w.astype(np.float32)
+
+
+def test_config1_full_size_against_the_reference_writer_and_forward():
+    """The single-linear benchmark configuration as stated (Student-t(5) seed 0, std 0.02,
+    k-means codebook, two-sided 99.95 % sidecar, no affine, x[1, 4096] fp32): the reference
+    writer's codebook and sidecar are in the golden file, its 16 MB index matrix is pinned by
+    hash, and reconstruct() / HelixLinear.forward by rows, row sums and the output."""
+    import hashlib
+    g = load_golden("config1_4096x4096")
+    w = _config1_weight()
+    assert hashlib.sha256(w.tobytes()).digest() == bytes(g["weight_sha256"])
+    idx = O.assign_sorted(w.ravel(), g["codebook"])
+    assert hashlib.sha256(idx.tobytes()).digest() == bytes(g["indices_sha256"])
+    rows = g["rows"]
+    # the reference's own assignment rule on the recorded rows
+    assert np.array_equal(O.chunked_assign(w[rows].ravel(), g["codebook"]), idx.reshape(4096, 4096)[rows].ravel())
+    idx = idx.reshape(4096, 4096)
+    pos, vals = O.find_outliers_percentile(w, 99.95)
+    assert np.array_equal(pos, g["sidecar_positions"])
+    assert np.array_equal(O.sidecar_fp16_roundtrip(vals), g["sidecar_values"])
+    rec = O.reconstruct(g["codebook"], idx, g["sidecar_positions"], g["sidecar_values"])
+    assert np.array_equal(rec[rows], g["reconstruct_rows"])
+    assert np.array_equal(rec.astype(np.float64).sum(1), g["reconstruct_row_sums_f64"])
+    r, c, d = O.derive_sidecar(g["codebook"], idx, g["sidecar_positions"], g["sidecar_values"])
+    y = O.forward_naive(g["x"], g["codebook"], idx, r, c, d)
+    assert np.allclose(y, g["y_naive"], atol=1e-5, rtol=1e-5)
+    assert rel_l2(y, g["y_forward"]) < 1e-5
