@@ -7,7 +7,11 @@ step runs RMSNorm (+ residual add), RoPE + KV-cache append, single-query
 grouped attention and SwiGLU as one launch each (decode_ops: 13 launches per
 layer) and is replayed from a CUDA graph; the prompt is prefilled with the same
 operators written in plain torch ops (also the parity reference of the step).  Tensor parallel: q/k/v/gate/up are
-column-parallel, o/down row-parallel with one all-reduce each (NCCL).
+column-parallel, o/down row-parallel with one sum over ranks each (NCCL, or the one-shot
+peer-memory kernel in the fused step).  Attention heads follow ``tp.head_partition``: when the
+ranks outnumber the KV heads (Qwen2.5-7B on 8 GPUs: 28 query / 4 KV heads) each KV head lives
+on two ranks and its seven query heads are dealt 4 + 3; the MLP is cut on whole 128-column
+affine groups.
 
 Weights are random-init (N(0, 0.02)) and compressed on the GPU; lm_head and the
 embedding stay dense bf16, as in the reference's policy (tensor_policy.py:199-208).
@@ -25,7 +29,7 @@ import torch.nn.functional as F
 from . import decode_ops
 from .helix_linear import HelixLinear
 from .hxq_writer_gpu import compress_weight
-from .tp import shard_helix_linear
+from .tp import head_partition, shard_bounds, take_cols, take_rows
 
 
 @dataclass
@@ -53,59 +57,118 @@ class Qwen2Shape:
         return Qwen2Shape(hidden=256, inter=512, layers=2, heads=4, kv_heads=2, head_dim=64, vocab=1024)
 
 
-def _hxq_linear(out_f: int, in_f: int, seed: int, device, bias: bool, group_size: int, name: str,
-                mode: Optional[str], rank: int, world: int) -> HelixLinear:
+def _compress_random(rows: int, cols: int, seed: int, device, bias: bool, group_size: int, name: str) -> HelixLinear:
+    """N(0, 0.02) weights of the given shape, compressed on the device."""
     g = torch.Generator(device=device).manual_seed(seed)
-    w = torch.randn(out_f, in_f, device=device, generator=g) * 0.02
-    b = (torch.randn(out_f, device=device, generator=g) * 0.02) if bias else None
-    enc = compress_weight(w, percentile=99.95, group_size=group_size)
-    del w
-    mod = HelixLinear(in_f, out_f, bias=b, tensor_name=name, **enc)
-    if world > 1 and mode is not None:
-        mod = shard_helix_linear(mod, mode, rank, world).to(device)
-    return mod
-
-
-def _hxq_fused_columns(outs, in_f: int, seed: int, device, bias: bool, group_size: int, name: str,
-                       rank: int, world: int) -> HelixLinear:
-    """Several column-parallel projections of one input as ONE compressed matrix (rows concatenated,
-    one codebook): this rank's slice of each, generated at its local size."""
-    rows = sum(o // world for o in outs)
-    g = torch.Generator(device=device).manual_seed(seed * 64 + rank)
-    w = torch.randn(rows, in_f, device=device, generator=g) * 0.02
+    w = torch.randn(rows, cols, device=device, generator=g) * 0.02
     b = (torch.randn(rows, device=device, generator=g) * 0.02) if bias else None
     enc = compress_weight(w, percentile=99.95, group_size=group_size)
     del w
-    return HelixLinear(in_f, rows, bias=b, tensor_name=name, **enc)
+    return HelixLinear(cols, rows, bias=b, tensor_name=name, **enc)
+
+
+MLP_CUT = 128   # the intermediate dimension is dealt to ranks in whole affine groups
 
 
 class Qwen2Layer(nn.Module):
-    def __init__(self, shp: Qwen2Shape, li: int, device, group_size: int, rank: int, world: int, fuse: bool = True):
+    """One decoder layer's HXQ projections for ``rank`` of ``world``.
+
+    ``build="global"`` compresses each full-size matrix and takes this rank's rows / columns of
+    it (exact tensor-parallel semantics: the shards of all ranks recompose the unsharded layer;
+    every rank pays for the whole matrix).  ``build="local"`` draws and compresses matrices of the
+    shard's own shape (random-init benchmarks: same shapes, 1/world of the encoding work)."""
+
+    def __init__(self, shp: Qwen2Shape, li: int, device, group_size: int, rank: int, world: int, fuse: bool = True,
+                 build: str = "local"):
         super().__init__()
-        H, D = shp.hidden, shp.head_dim
-        if shp.heads % world or shp.kv_heads % world:
-            raise ValueError(f"tensor-parallel {world} does not divide {shp.heads} query / {shp.kv_heads} KV heads")
-        p = f"model.layers.{li}"
-        mk = lambda o, i, k, bias, name, mode: _hxq_linear(o, i, 1000 * li + k, device, bias, group_size,
-                                                           f"{p}.{name}.weight", mode, rank, world)
+        if build not in ("local", "global"):
+            raise ValueError(f"build must be 'local' or 'global', got {build!r}")
+        H, D, Hq, Hkv, I = shp.hidden, shp.head_dim, shp.heads, shp.kv_heads, shp.inter
+        q0, q1, kv0, kv1 = head_partition(Hq, Hkv, world)[rank]
+        i0, i1 = shard_bounds(I, rank, world, MLP_CUT if world > 1 else 1)
+        if i1 <= i0:
+            raise ValueError(f"tensor-parallel {world}: rank {rank} would hold no MLP columns of {I}")
+        self.n_q, self.n_kv, self.inter_local = q1 - q0, kv1 - kv0, i1 - i0
+        nq, nkv, ni = self.n_q, self.n_kv, self.inter_local
+        p, sd = f"model.layers.{li}", 1000 * li
         self.fused = fuse
+        glob = build == "global"
+        rseed = 0 if glob else 64 + rank       # local builds differ per rank
+        mk = lambda rows, cols, k, bias, name: _compress_random(rows, cols, (sd + k) * 128 + rseed, device, bias,
+                                                                group_size, f"{p}.{name}.weight")
         if fuse:   # q|k|v and gate|up as one compressed matrix each: 4 products per layer instead of 7
-            self.qkv_proj = _hxq_fused_columns([shp.heads * D, shp.kv_heads * D, shp.kv_heads * D], H, 1000 * li + 7,
-                                               device, True, group_size, f"{p}.self_attn.qkv_proj.weight", rank, world)
-            self.gate_up_proj = _hxq_fused_columns([shp.inter, shp.inter], H, 1000 * li + 8, device, False, group_size,
-                                                   f"{p}.mlp.gate_up_proj.weight", rank, world)
+            if glob:
+                qkv = mk((Hq + 2 * Hkv) * D, H, 7, True, "self_attn.qkv_proj")
+                self.qkv_proj = take_rows(qkv, [(q0 * D, q1 * D), ((Hq + kv0) * D, (Hq + kv1) * D),
+                                                ((Hq + Hkv + kv0) * D, (Hq + Hkv + kv1) * D)]).to(device)
+                gu = mk(2 * I, H, 8, False, "mlp.gate_up_proj")
+                self.gate_up_proj = take_rows(gu, [(i0, i1), (I + i0, I + i1)]).to(device)
+                del qkv, gu
+            else:
+                self.qkv_proj = mk((nq + 2 * nkv) * D, H, 7, True, "self_attn.qkv_proj")
+                self.gate_up_proj = mk(2 * ni, H, 8, False, "mlp.gate_up_proj")
         else:
-            self.q_proj = mk(shp.heads * D, H, 0, True, "self_attn.q_proj", "column")
-            self.k_proj = mk(shp.kv_heads * D, H, 1, True, "self_attn.k_proj", "column")
-            self.v_proj = mk(shp.kv_heads * D, H, 2, True, "self_attn.v_proj", "column")
-            self.gate_proj = mk(shp.inter, H, 4, False, "mlp.gate_proj", "column")
-            self.up_proj = mk(shp.inter, H, 5, False, "mlp.up_proj", "column")
-        self.o_proj = mk(H, shp.heads * D, 3, False, "self_attn.o_proj", "row")
-        self.down_proj = mk(H, shp.inter, 6, False, "mlp.down_proj", "row")
-        self.inter_local = shp.inter // world
+            cut = lambda m, a, b: take_rows(m, [(a, b)]).to(device)
+            if glob:
+                self.q_proj = cut(mk(Hq * D, H, 0, True, "self_attn.q_proj"), q0 * D, q1 * D)
+                self.k_proj = cut(mk(Hkv * D, H, 1, True, "self_attn.k_proj"), kv0 * D, kv1 * D)
+                self.v_proj = cut(mk(Hkv * D, H, 2, True, "self_attn.v_proj"), kv0 * D, kv1 * D)
+                self.gate_proj = cut(mk(I, H, 4, False, "mlp.gate_proj"), i0, i1)
+                self.up_proj = cut(mk(I, H, 5, False, "mlp.up_proj"), i0, i1)
+            else:
+                self.q_proj = mk(nq * D, H, 0, True, "self_attn.q_proj")
+                self.k_proj = mk(nkv * D, H, 1, True, "self_attn.k_proj")
+                self.v_proj = mk(nkv * D, H, 2, True, "self_attn.v_proj")
+                self.gate_proj = mk(ni, H, 4, False, "mlp.gate_proj")
+                self.up_proj = mk(ni, H, 5, False, "mlp.up_proj")
+        if glob:
+            self.o_proj = take_cols(mk(H, Hq * D, 3, False, "self_attn.o_proj"), q0 * D, q1 * D).to(device)
+            self.down_proj = take_cols(mk(H, I, 6, False, "mlp.down_proj"), i0, i1).to(device)
+        else:
+            self.o_proj = mk(H, nq * D, 3, False, "self_attn.o_proj")
+            self.down_proj = mk(H, ni, 6, False, "mlp.down_proj")
         self.ln1 = nn.Parameter(torch.ones(H, device=device, dtype=torch.bfloat16), requires_grad=False)
         self.ln2 = nn.Parameter(torch.ones(H, device=device, dtype=torch.bfloat16), requires_grad=False)
-        self.n_q, self.n_kv = shp.heads // world, shp.kv_heads // world
+
+
+def _drive(gen, reduce):
+    """Run a block generator: it yields ``(partial, key)`` wherever a sum over the tensor-parallel
+    ranks is due and is sent the summed tensor back."""
+    try:
+        item = next(gen)
+        while True:
+            item = gen.send(reduce(*item))
+    except StopIteration as e:
+        return e.value
+
+
+def run_ranks_in_process(gens):
+    """Drive the block generators of ALL ranks of a tensor-parallel group inside one process, in
+    lockstep: at every exchange point the partials are added in rank order in fp32 and rounded
+    once to bf16, which is what the one-shot peer-memory kernel does.  This is how the sharded
+    decoder is checked against the unsharded one on a single GPU.  Returns each rank's result."""
+    results = [None] * len(gens)
+    try:
+        items = [next(g) for g in gens]
+    except StopIteration:
+        raise RuntimeError("a rank finished before its first exchange")
+    while True:
+        total = items[0][0].float().clone()
+        for part, _ in items[1:]:
+            total += part.float()
+        total = total.to(torch.bfloat16)
+        nxt, done = [], 0
+        for r, g in enumerate(gens):
+            try:
+                nxt.append(g.send(total.clone()))
+            except StopIteration as e:
+                results[r] = e.value
+                done += 1
+        if done == len(gens):
+            return results
+        if done:
+            raise RuntimeError("ranks disagree on the number of exchanges")
+        items = nxt
 
 
 class Qwen2HxqDecoder(nn.Module):
@@ -113,17 +176,18 @@ class Qwen2HxqDecoder(nn.Module):
     ``step`` decodes one token per sequence at ``pos`` (a device scalar)."""
 
     def __init__(self, shp: Qwen2Shape, device, batch: int, max_len: int, group_size: int = 128,
-                 rank: int = 0, world: int = 1, group=None, fuse_proj: bool = True, p2p_allreduce: bool = False):
+                 rank: int = 0, world: int = 1, group=None, fuse_proj: bool = True, p2p_allreduce: bool = False,
+                 build: str = "local"):
         super().__init__()
         self.shp, self.device, self.world, self.group = shp, device, world, group
         self.p2p = bool(p2p_allreduce) and world > 1   # one-shot peer-memory sum instead of NCCL in the fused step
-        self.layers = nn.ModuleList(Qwen2Layer(shp, i, device, group_size, rank, world, fuse_proj)
+        self.layers = nn.ModuleList(Qwen2Layer(shp, i, device, group_size, rank, world, fuse_proj, build)
                                     for i in range(shp.layers))
         g = torch.Generator(device=device).manual_seed(7)
         self.embed = (torch.randn(shp.vocab, shp.hidden, device=device, generator=g) * 0.02).bfloat16()
         self.lm_head = (torch.randn(shp.vocab, shp.hidden, device=device, generator=g) * 0.02).bfloat16()
         self.norm = torch.ones(shp.hidden, device=device, dtype=torch.bfloat16)
-        n_kv = shp.kv_heads // world
+        n_kv = self.layers[0].n_kv
         self.k_cache = torch.zeros(shp.layers, batch, n_kv, max_len, shp.head_dim, device=device, dtype=torch.bfloat16)
         self.v_cache = torch.zeros_like(self.k_cache)
         inv = 1.0 / (shp.rope_theta ** (torch.arange(0, shp.head_dim, 2, device=device, dtype=torch.float32)
@@ -152,6 +216,12 @@ class Qwen2HxqDecoder(nn.Module):
         """ids [B, T]; positions [T] (absolute); the new K/V go to cache rows
         ``cache_rows`` [T]; attention spans cache[:attn_len] (None = whole cache
         with a position mask, which is what the captured one-token step uses)."""
+        return _drive(self.blocks_tokens(ids, positions, cache_rows, attn_len), lambda part, key: self._allreduce(part))
+
+    def blocks_tokens(self, ids: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor,
+                      attn_len: Optional[int]):
+        """``forward_tokens`` as a generator: yields ``(partial [B, T, hidden], key)`` after o_proj and
+        down_proj of every layer and expects the sum over ranks back; returns the logits."""
         B, T = ids.shape
         D = self.shp.head_dim
         h = self.embed[ids]
@@ -176,13 +246,13 @@ class Qwen2HxqDecoder(nn.Module):
                 mask = (torch.arange(attn_len, device=ids.device)[None, :] <= positions[:, None])[None, None]
             a = F.scaled_dot_product_attention(q, kk, vv, attn_mask=mask, enable_gqa=True)
             a = a.transpose(1, 2).reshape(B, T, L.n_q * D)
-            h = h + self._allreduce(L.o_proj(a))
+            h = h + (yield L.o_proj(a), "d1")
             x = self._rms(h, L.ln2)
             if L.fused:
                 gt, up = L.gate_up_proj(x).split([L.inter_local, L.inter_local], -1)
             else:
                 gt, up = L.gate_proj(x), L.up_proj(x)
-            h = h + self._allreduce(L.down_proj(F.silu(gt) * up))
+            h = h + (yield L.down_proj(F.silu(gt) * up), "d2")
         h = self._rms(h[:, -1], self.norm)
         return h @ self.lm_head.t()
 
@@ -201,17 +271,23 @@ class Qwen2HxqDecoder(nn.Module):
             self._sb = sb
         return sb
 
-    def _row_parallel(self, lin: HelixLinear, x: torch.Tensor, sb: dict, out_key: str) -> torch.Tensor:
-        """Row-parallel product + the sum over ranks, result in bf16 in sb[out_key]."""
+    def _reduce_step(self, part: torch.Tensor, key: str) -> torch.Tensor:
+        """Sum of one step's row-parallel partial over the ranks, bf16 result in the step buffer ``key``."""
+        sb = self._sb
         if self.p2p:
-            lin.packed().matmul(x, torch.float32, out=sb["p32"])
-            return self._ar(sb["p32"], out=sb[out_key])
-        return self._allreduce(lin.packed().matmul(x, torch.bfloat16, out=sb[out_key]))
+            return self._ar(part, out=sb[key])
+        return self._allreduce(part)
 
     def step_fused(self, tok: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         """One decode step for tok [B, 1] at position pos (int64 device tensor [1]): same
         arithmetic as ``forward_tokens(tok, pos, pos, None)`` with the glue between the
         linears in four fused operators.  Returns the logits [B, vocab]."""
+        return _drive(self.blocks_step(tok, pos, fp32_partials=self.p2p), self._reduce_step)
+
+    def blocks_step(self, tok: torch.Tensor, pos: torch.Tensor, fp32_partials: bool = False):
+        """``step_fused`` as a generator: yields ``(partial [B, hidden], key)`` after o_proj and down_proj
+        of every layer (fp32 when the sum is taken by the one-shot kernel or in process, bf16 for NCCL)
+        and expects the bf16 sum over ranks back; returns the logits."""
         B = tok.shape[0]
         sb = self._step_buffers(B)
         D, eps = self.shp.head_dim, self.shp.rms_eps
@@ -219,6 +295,14 @@ class Qwen2HxqDecoder(nn.Module):
         h, x = sb["h"], sb["x"]
         h.copy_(self.embed[tok[:, 0]])
         delta = None
+
+        def row_parallel(lin, xin, key):
+            if fp32_partials:
+                if "p32" not in sb:
+                    sb["p32"] = torch.empty(B, self.shp.hidden, device=self.device, dtype=torch.float32)
+                return lin.packed().matmul(xin, torch.float32, out=sb["p32"]), key
+            return lin.packed().matmul(xin, bf, out=sb[key]), key
+
         for li, L in enumerate(self.layers):
             nq, nkv = L.n_q, L.n_kv
             decode_ops.add_rmsnorm(h, delta, L.ln1, eps, x)
@@ -231,7 +315,7 @@ class Qwen2HxqDecoder(nn.Module):
                 L.v_proj.packed().matmul(x, bf, out=qkv[:, (nq + nkv) * D:])
             decode_ops.rope_append(qkv, pos, self.cos, self.sin, sb["q"], self.k_cache[li], self.v_cache[li], nq, nkv)
             decode_ops.attn_decode(sb["q"], self.k_cache[li], self.v_cache[li], pos, sb["a"], nq, D ** -0.5)
-            delta = self._row_parallel(L.o_proj, sb["a"], sb, "d1")
+            delta = yield row_parallel(L.o_proj, sb["a"], "d1")
             decode_ops.add_rmsnorm(h, delta, L.ln2, eps, x)
             if L.fused:
                 L.gate_up_proj.packed().matmul(x, bf, out=gu)
@@ -239,7 +323,7 @@ class Qwen2HxqDecoder(nn.Module):
                 L.gate_proj.packed().matmul(x, bf, out=gu[:, :ni])
                 L.up_proj.packed().matmul(x, bf, out=gu[:, ni:])
             decode_ops.swiglu(gu[:, :ni], gu[:, ni:], sb["act"])
-            delta = self._row_parallel(L.down_proj, sb["act"], sb, "d2")
+            delta = yield row_parallel(L.down_proj, sb["act"], "d2")
         decode_ops.add_rmsnorm(h, delta, self.norm, eps, x)
         return x @ self.lm_head.t()
 
@@ -266,15 +350,19 @@ class Qwen2HxqDecoder(nn.Module):
                 return self.step_fused(tok, pos).argmax(-1)
             return self.forward_tokens(tok, pos, pos, None).argmax(-1)
 
+        # warm up on the stream the capture will run on: the kernels' workspaces are kept per
+        # stream and must exist (and be zero) before the capture starts
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
             for _ in range(2):
                 body()
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                out = body()
         torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            out = body()
+        self._graph = graph
 
         def run():
             graph.replay()
@@ -321,6 +409,8 @@ def main(argv=None):
     ap.add_argument("--torch-glue", action="store_true", help="run the step's glue in plain torch ops")
     ap.add_argument("--allreduce", default="p2p", choices=["nccl", "p2p"],
                     help="tensor-parallel sum in the fused step: NCCL, or the one-shot peer-memory kernel")
+    ap.add_argument("--build", default="local", choices=["local", "global"],
+                    help="local: each rank compresses matrices of its shard's shape; global: full matrices, then sharded")
     ap.add_argument("--separate-proj", action="store_true",
                     help="q, k, v and gate, up as separate compressed matrices (7 products per layer instead of 4)")
     args = ap.parse_args(argv)
@@ -330,13 +420,17 @@ def main(argv=None):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # plain peer-to-peer only: no buffer of this process is ever bound to an NVLink multicast
+        # object (a rank that goes away while bound to one takes its peers' GPUs with it)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.distributed.init_process_group("nccl", device_id=dev)
     shp = {"7b": Qwen2Shape.qwen25_7b, "14b": Qwen2Shape.qwen25_14b, "tiny": Qwen2Shape.tiny}[args.shape]()
     if args.layers:
         shp.layers = args.layers
     t0 = time.perf_counter()
     model = Qwen2HxqDecoder(shp, dev, args.batch, args.prompt + args.new + 8, rank=rank, world=world,
-                            fuse_proj=not args.separate_proj, p2p_allreduce=args.allreduce == "p2p")
+                            fuse_proj=not args.separate_proj, p2p_allreduce=args.allreduce == "p2p", build=args.build)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     prompt = torch.randint(0, shp.vocab, (args.batch, args.prompt), device=dev,
@@ -387,12 +481,37 @@ def main(argv=None):
             "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,
             "data": "synthetic: N(0,0.02) weights, uniform random prompt ids",
         }), flush=True)
-    if world > 1:   # no process-group teardown while graphs holding its collectives are alive (it blocks)
-        import sys
-        torch.cuda.synchronize()
-        torch.distributed.barrier()
-        sys.stdout.flush()
-        os._exit(0)
+    if world > 1:
+        leave_process_group(model)
+
+
+def leave_process_group(*holders) -> None:
+    """End a multi-rank run: every rank has finished its GPU work, the captured graphs that hold
+    collectives are dropped first (tearing the group down under a live graph blocks), then the
+    group is destroyed.  If that still does not return within a minute the process exits anyway -
+    after the barrier, with nothing in flight and NVLS off."""
+    import gc
+    import os
+    import sys
+    import threading
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    torch.cuda.synchronize()
+    for h in holders:
+        for name in ("_graph", "_ar", "_sb"):
+            if hasattr(h, name):
+                try:
+                    delattr(h, name)
+                except AttributeError:
+                    pass
+    gc.collect()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    t = threading.Timer(60.0, lambda: os._exit(0))
+    t.daemon = True
+    t.start()
+    torch.distributed.destroy_process_group()
+    t.cancel()
 
 
 if __name__ == "__main__":

@@ -20,44 +20,57 @@ from .helix_linear import HelixLinear
 
 
 def shard_bounds(n: int, rank: int, world: int, multiple: int = 1) -> Tuple[int, int]:
-    """Contiguous slice [a, b) of ``n`` for ``rank``; every slice but the last
-    has ceil(n / world) rounded up to ``multiple`` elements."""
-    per = -(-n // world)
-    per = -(-per // multiple) * multiple
-    return min(rank * per, n), min((rank + 1) * per, n)
+    """Contiguous slice [a, b) of ``n`` for ``rank``: ``n`` is dealt in units of ``multiple``
+    elements as evenly as they go (the first ranks hold one unit more; the last slice ends at n)."""
+    units = -(-n // multiple)
+    base, extra = divmod(units, world)
+    a = (rank * base + min(rank, extra)) * multiple
+    b = ((rank + 1) * base + min(rank + 1, extra)) * multiple
+    return min(a, n), min(b, n)
 
 
-def shard_helix_linear(mod: HelixLinear, mode: str, rank: int, world: int) -> HelixLinear:
-    """The shard of ``mod`` that ``rank`` of ``world`` holds.
-
-    ``mode="column"``: rows [r0, r1) of the weight (outputs split).
-    ``mode="row"``:   columns [c0, c1) (inputs split, 16-column granularity);
-    the result carries ``col0 = c0`` and is a partial sum - use
-    RowParallelHelixLinear (or all-reduce yourself).  Bias stays on rank 0."""
-    if mode not in ("column", "row"):
-        raise ValueError(f"mode must be 'column' or 'row', got {mode!r}")
+def take_rows(mod: HelixLinear, ranges) -> HelixLinear:
+    """A new HelixLinear holding the output rows ``[(r0, r1), ...]`` of ``mod``, concatenated in
+    the order given (one codebook, so several projections compressed jointly - q|k|v, gate|up -
+    shard by picking each one's rows).  Sidecar positions are row-major and sorted, so each range
+    is one contiguous run of them."""
     if mod.has_svd or mod.has_channel_scales:
         raise NotImplementedError("SVD residual / channel scales are not sharded")
-    n_out, n_in, G = mod.out_features, mod.in_features, mod.group_size
-    idx = mod.indices
-    pos, vals = mod.sidecar_positions, mod.sidecar_values
+    n_in, G = mod.in_features, mod.group_size
+    ranges = [(int(a), int(b)) for a, b in ranges if b > a]
+    idx = torch.cat([mod.indices[a:b] for a, b in ranges]).contiguous()
     kw = {}
-    if mode == "column":
-        r0, r1 = shard_bounds(n_out, rank, world)
-        new_idx = idx[r0:r1].contiguous()
-        if pos is not None:
-            keep = (pos >= r0 * n_in) & (pos < r1 * n_in)
-            kw.update(sidecar_positions=(pos[keep] - r0 * n_in).contiguous(), sidecar_values=vals[keep].contiguous())
-        if mod.group_scales is not None:
-            kw.update(group_scales=mod.group_scales[r0:r1].contiguous(),
-                      group_offsets=mod.group_offsets[r0:r1].contiguous(), group_size=G)
-        bias = None if mod.bias is None else mod.bias[r0:r1].contiguous()
-        out = HelixLinear(n_in, r1 - r0, mod.codebook, new_idx, bias=bias, tensor_name=mod.tensor_name,
-                          compute_dtype=mod.compute_dtype, **kw)
-        out.tp_mode, out.tp_slice = "column", (r0, r1)
-        return out
-    c0, c1 = shard_bounds(n_in, rank, world, multiple=16)
-    new_idx = idx[:, c0:c1].contiguous()
+    pos, vals = mod.sidecar_positions, mod.sidecar_values
+    if pos is not None:
+        ps, vs, base = [], [], 0
+        for a, b in ranges:
+            lo, hi = torch.searchsorted(pos, torch.tensor([a * n_in, b * n_in], device=pos.device)).tolist()
+            ps.append(pos[lo:hi] - a * n_in + base * n_in)
+            vs.append(vals[lo:hi])
+            base += b - a
+        kw.update(sidecar_positions=torch.cat(ps).contiguous(), sidecar_values=torch.cat(vs).contiguous())
+    if mod.group_scales is not None:
+        kw.update(group_scales=torch.cat([mod.group_scales[a:b] for a, b in ranges]).contiguous(),
+                  group_offsets=torch.cat([mod.group_offsets[a:b] for a, b in ranges]).contiguous(), group_size=G)
+    bias = None if mod.bias is None else torch.cat([mod.bias[a:b] for a, b in ranges]).contiguous()
+    out = HelixLinear(n_in, idx.shape[0], mod.codebook, idx, bias=bias, tensor_name=mod.tensor_name,
+                      compute_dtype=mod.compute_dtype, **kw)
+    out.tp_mode, out.tp_slice = "column", ranges
+    return out
+
+
+def take_cols(mod: HelixLinear, c0: int, c1: int, keep_bias: bool = True) -> HelixLinear:
+    """A new HelixLinear over input columns [c0, c1) of ``mod`` (a partial sum of the full
+    product).  ``c0`` must be a multiple of 16; the result carries ``col0 = c0`` so that affine
+    group ids stay global, and the groups cut by the bounds live on both neighbours."""
+    if mod.has_svd or mod.has_channel_scales:
+        raise NotImplementedError("SVD residual / channel scales are not sharded")
+    if c0 % 16:
+        raise ValueError("column shards start on a multiple of 16")
+    n_out, n_in, G = mod.out_features, mod.in_features, mod.group_size
+    kw = {}
+    new_idx = mod.indices[:, c0:c1].contiguous()
+    pos, vals = mod.sidecar_positions, mod.sidecar_values
     if pos is not None:
         rows, cols = pos // n_in, pos % n_in
         keep = (cols >= c0) & (cols < c1)
@@ -67,7 +80,7 @@ def shard_helix_linear(mod: HelixLinear, mode: str, rank: int, world: int) -> He
         g0, g1 = c0 // G, (c1 - 1) // G + 1   # boundary groups are duplicated on both neighbours
         kw.update(group_scales=mod.group_scales[:, g0:g1].contiguous(),
                   group_offsets=mod.group_offsets[:, g0:g1].contiguous(), group_size=G)
-    bias = mod.bias if rank == 0 else None
+    bias = mod.bias if keep_bias else None
     out = HelixLinear.__new__(HelixLinear)
     nn.Module.__init__(out)
     out._init_attrs(c1 - c0, n_out, mod.tensor_name, mod.compute_dtype, 1)
@@ -84,6 +97,60 @@ def shard_helix_linear(mod: HelixLinear, mode: str, rank: int, world: int) -> He
         out.register_buffer(name, None, persistent=False)
     out._derive()
     out.tp_mode, out.tp_slice = "row", (c0, c1)
+    return out
+
+
+def shard_helix_linear(mod: HelixLinear, mode: str, rank: int, world: int,
+                       multiple: Optional[int] = None) -> HelixLinear:
+    """The shard of ``mod`` that ``rank`` of ``world`` holds.
+
+    ``mode="column"``: rows [r0, r1) of the weight (outputs split).
+    ``mode="row"``:   columns [c0, c1) (inputs split, 16-column granularity);
+    the result carries ``col0 = c0`` and is a partial sum - use
+    RowParallelHelixLinear (or all-reduce yourself).  Bias stays on rank 0.
+
+    ``multiple`` rounds every shard but the last up to that many rows / columns (default 1 for
+    rows, 16 for columns).  A column-parallel layer feeding a row-parallel one must be cut with
+    the same value; cutting an MLP at ``multiple=128`` keeps every shard of ``down`` on whole
+    affine groups, which is the shape the streaming kernel is fastest on."""
+    if mode not in ("column", "row"):
+        raise ValueError(f"mode must be 'column' or 'row', got {mode!r}")
+    if mode == "column":
+        r0, r1 = shard_bounds(mod.out_features, rank, world, multiple or 1)
+        out = take_rows(mod, [(r0, r1)])
+        out.tp_slice = (r0, r1)
+        return out
+    if multiple is not None and multiple % 16:
+        raise ValueError("column shards are cut at multiples of 16")
+    c0, c1 = shard_bounds(mod.in_features, rank, world, multiple or 16)
+    return take_cols(mod, c0, c1, keep_bias=(rank == 0))
+
+
+def head_partition(heads: int, kv_heads: int, world: int):
+    """Attention heads per tensor-parallel rank: a list of ``(q0, q1, kv0, kv1)``, rank r owning
+    query heads [q0, q1) and KV heads [kv0, kv1).
+
+    While ``world`` divides the KV heads every rank gets whole KV groups.  Beyond that
+    (``world`` a multiple of the KV heads, e.g. 28 query / 4 KV heads on 8 GPUs) each KV head is
+    held by ``world / kv_heads`` ranks and its query heads are dealt over them as evenly as
+    they go (7 -> 4 + 3): ranks then differ by one query head, nothing is padded, and the
+    row-parallel o_proj sums partials of different input widths."""
+    if heads % kv_heads:
+        raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} KV heads")
+    gq = heads // kv_heads
+    if kv_heads % world == 0:
+        k = kv_heads // world
+        return [(r * k * gq, (r + 1) * k * gq, r * k, (r + 1) * k) for r in range(world)]
+    if world % kv_heads:
+        raise ValueError(f"tensor-parallel {world} neither divides nor is a multiple of {kv_heads} KV heads")
+    rep = world // kv_heads
+    if rep > gq:
+        raise ValueError(f"{world} ranks for {heads} query heads: some rank would hold none")
+    per = -(-gq // rep)
+    out = []
+    for r in range(world):
+        kv, j = r // rep, r % rep
+        out.append((kv * gq + min(j * per, gq), kv * gq + min((j + 1) * per, gq), kv, kv + 1))
     return out
 
 

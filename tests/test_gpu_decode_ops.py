@@ -126,3 +126,45 @@ def test_fused_step_matches_the_torch_step(fuse_proj):
     with torch.no_grad():
         toks = model.greedy_decode(prompt, 8, graphed=True)
     assert toks.shape == (2, 8) and int(toks.min()) >= 0 and int(toks.max()) < 1024
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_decoder_matches_the_unsharded_one_on_one_gpu(world):
+    """Tensor-parallel decoding with more ranks than KV heads (14 query / 2 KV heads on 4 ranks: the
+    28 / 4 on 8 layout of Qwen2.5-7B), every rank's shard cut from the SAME compressed matrices.
+    All ranks run inside this process on one GPU, their row-parallel partials summed where the
+    exchange would be: prefill logits, one fused step's logits and the KV caches must agree with
+    the unsharded decoder to bf16 precision."""
+    from helix_substrate_b200.qwen2_decode import Qwen2HxqDecoder, Qwen2Shape, run_ranks_in_process
+    from helix_substrate_b200.tp import head_partition
+    dev = _dev()
+    shp = Qwen2Shape(hidden=256, inter=640, layers=2, heads=14, kv_heads=2, head_dim=64, vocab=512)
+    B, T, max_len = 2, 37, 64
+    full = Qwen2HxqDecoder(shp, dev, batch=B, max_len=max_len, build="global")
+    ranks = [Qwen2HxqDecoder(shp, dev, batch=B, max_len=max_len, rank=r, world=world, build="global")
+             for r in range(world)]
+    prompt = torch.randint(0, shp.vocab, (B, T), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    pos = torch.arange(T, device=dev)
+    with torch.no_grad():
+        ref = full.forward_tokens(prompt, pos, pos, T)
+        outs = run_ranks_in_process([m.blocks_tokens(prompt, pos, pos, T) for m in ranks])
+    for o in outs:
+        assert torch.equal(o, outs[0]), "every rank must end with the same logits"
+    assert rel_l2(outs[0].float().cpu(), ref.float().cpu()) < 3e-2
+    parts = head_partition(shp.heads, shp.kv_heads, world)
+    for r, m in enumerate(ranks):   # each rank's cache holds exactly its KV heads
+        kv0, kv1 = parts[r][2], parts[r][3]
+        assert m.k_cache.shape[2] == kv1 - kv0
+        assert rel_l2(m.k_cache[:, :, :, :T].float().cpu(), full.k_cache[:, :, kv0:kv1, :T].float().cpu()) < 2e-2
+        assert rel_l2(m.v_cache[:, :, :, :T].float().cpu(), full.v_cache[:, :, kv0:kv1, :T].float().cpu()) < 2e-2
+    # one fused decode step on top of those caches
+    tok = ref.argmax(-1)[:, None]
+    p1 = torch.tensor([T], device=dev)
+    with torch.no_grad():
+        ref_step = full.step_fused(tok, p1)
+        outs = run_ranks_in_process([m.blocks_step(tok, p1, fp32_partials=True) for m in ranks])
+    for o in outs:
+        assert torch.equal(o, outs[0])
+    assert rel_l2(outs[0].float().cpu(), ref_step.float().cpu()) < 3e-2
+    assert int(outs[0].argmax(-1)[0]) == int(ref_step.argmax(-1)[0]) or \
+        rel_l2(outs[0].float().cpu(), ref_step.float().cpu()) < 1e-2
