@@ -33,6 +33,13 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
                int64_t ldy, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemv_workspace_bytes(const hxq_desc* d, int32_t M);
 
+namespace gemmts {   // 17 .. 128 tokens: A operand through tensor memory (hxq_gemm_ts.cu)
+bool covers(const hxq_desc* d, int32_t M);
+size_t split_bytes(const hxq_desc* d, int32_t M);
+int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, void* y, int y_dtype, int64_t ldy,
+        void* split_ws, size_t split_ws_bytes, int32_t* status_word, cudaStream_t stream);
+}  // namespace gemmts
+
 namespace gemm {
 
 constexpr int BM = 128;        // output rows per CTA = UMMA M
@@ -358,7 +365,7 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-static bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
                         uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
@@ -391,6 +398,14 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
         if (bias != nullptr) v += bias[o];
         store_from_f32(y, (int64_t)m * ldy + o, v, y_dtype);
     }
+}
+
+void launch_splitk_reduce(const float* partial, int splits, int M, int out_features, const float* bias, void* y,
+                          int y_dtype, int64_t ldy, cudaStream_t stream) {
+    const int64_t total = (int64_t)M * out_features;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, splits, M, out_features, bias, y, y_dtype, ldy);
 }
 
 // K slices per output tile: enough CTAs to fill the GPU when the tile grid alone does not
@@ -431,6 +446,10 @@ size_t workspace_bytes(const hxq_desc* d, int32_t M) {
     const int BN = pick_bn(M);
     const int s = pick_splits((M + BN - 1) / BN, (d->out_features + BM - 1) / BM, (d->in_features + BK - 1) / BK, sm_count());
     if (s > 1) split = (size_t)s * M * d->out_features * sizeof(float);
+    if (gemmts::covers(d, M)) {
+        const size_t ts = gemmts::split_bytes(d, M);
+        split = ts > split ? ts : split;
+    }
     return xcopy_bytes(d, M) + split;
 }
 
@@ -467,6 +486,12 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
         if (cudaGetLastError() != cudaSuccess) return HXQ_E_LAUNCH;
         xb = workspace;
         ldxb = ld;
+    }
+    if (gemmts::covers(d, M)) {   // up to 128 tokens: the index-stream-bound kernel
+        const size_t off = xcopy_bytes(d, M);
+        void* sws = (workspace && ws_bytes > off) ? reinterpret_cast<char*>(workspace) + off : nullptr;
+        return gemmts::run(d, reinterpret_cast<const __nv_bfloat16*>(xb), ldxb, M, y, y_dtype, ldy, sws,
+                           sws ? ws_bytes - off : 0, status_word, stream);
     }
     const int BN = pick_bn(M);
     CUtensorMap mi, mx;
@@ -509,10 +534,7 @@ int run(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t ldx, v
     else if (BN == 128) st = launch<128>(mi, mx, a, grid_m, grid_o, splits, stream);
     else st = launch<64>(mi, mx, a, grid_m, grid_o, splits, stream);
     if (st != HXQ_OK || splits == 1) return st;
-    const int64_t total = (int64_t)M * d->out_features;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy);
+    launch_splitk_reduce(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy, stream);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 

@@ -1,0 +1,441 @@
+// hxq_gemm, 17 .. 128 tokens: y[m, o] = sum_i x[m, i] * W^[o, i] + sidecar + bias on the tensor cores
+// with the dequantised weights handed to the MMA through TENSOR MEMORY, never through shared memory.
+//
+// At these token counts the product is still bound by the index stream (one byte and one table lookup
+// per weight, each weight used for at most 128 tokens), so the kernel is built like the decode kernel,
+// not like a GEMM: everything that is not a lookup is kept off the shared-memory data path.
+//
+//   * CTA tile: 128 output rows x BN tokens (BN = 32, 64, 128), K walked in stages of 128 columns,
+//     one CTA per SM; small row-tile grids split K over gridDim.z (fp32 partials + a fixed-order sum).
+//   * warp 0, one lane: TMA producer.  Per stage one 128 x 128 box of index bytes and two 64-column
+//     boxes of bf16 activations, all 128-byte swizzled, on one mbarrier.  No multicast, no cluster.
+//   * warps 2..9: dequantisers, ONE THREAD PER OUTPUT ROW and 64-column half of the stage.  A thread
+//     reads its row's 64 codes with four conflict-free 16-byte loads (the swizzle spreads eight rows
+//     over all banks), looks each up in the lane-replicated codebook (one byte-permute + one load per
+//     weight, bank == lane), applies its (row, group) scale and offset in fp32, packs pairs to bf16
+//     and stores its 32 registers straight into the A operand's columns of tensor memory
+//     (tcgen05.st 32x32b: TMEM lane == output row).  Scale/offset, row pointer and sidecar cursor
+//     are thread-local: there is no cross-lane step anywhere.
+//   * warp 1, one lane: issues tcgen05.mma kind::f16 with A from tensor memory and B (activations,
+//     K-major, 128-byte swizzle) from shared memory into the fp32 accumulator in tensor memory, and
+//     commits the stage back to the producer.
+//   * epilogue (the dequantising warps): accumulator -> registers, + the row's sidecar entries as
+//     fp32 delta * x (a few entries per row: their activations come through L1/L2), + bias, store.
+//
+// Every mbarrier wait is clock-bounded; a wait that gives up raises a CTA-wide abort flag and the
+// global status word (HXQ_E_TIMEOUT), in-flight copies are given time to land and tensor memory is
+// freed before the CTA returns.
+
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "hxq_common.cuh"
+#include "hxq_sm100.cuh"
+
+namespace hxq {
+namespace gemm {   // helpers shared with the large-token kernel (hxq_gemm.cu)
+bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                 uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw);
+void launch_splitk_reduce(const float* partial, int splits, int M, int out_features, const float* bias, void* y,
+                          int y_dtype, int64_t ldy, cudaStream_t stream);
+}  // namespace gemm
+
+namespace gemmts {
+
+constexpr int BM = 128;             // output rows per CTA = UMMA M = TMEM lanes
+constexpr int KS = 128;             // K columns per stage
+constexpr int DEQ_WARPS = 8;        // warps w and w + 4 share a TMEM lane quarter and split the stage's K halves
+constexpr int NUM_THREADS = 32 * (2 + DEQ_WARPS);
+constexpr int LUT_BYTES = 256 * 256;            // entry c, lane l at c * 256 + l * 4, base on a 64 KB boundary
+constexpr int IDX_BYTES = BM * KS;              // 16 KB
+constexpr int SMEM_TOTAL = 232448;
+constexpr int MAX_STAGES = 4;
+constexpr int TMEM_COLS = 512;
+constexpr int A_COLS = KS / 2;                  // 64 columns of packed bf16 pairs per stage
+
+struct Args {
+    const float* cb;
+    const void* scales;
+    const void* offsets;
+    const int32_t* rowptr;
+    const int32_t* cols;
+    const float* deltas;
+    const float* bias;
+    const __nv_bfloat16* xb;   // activations as bf16 [M, ldxb] (the sidecar reads them directly)
+    void* y;
+    int32_t* status;
+    float* partial;            // [splits][M][out_features] when the K range is split, else nullptr
+    int64_t ldy, ldxb;
+    int32_t out_features, in_features, col0, group_size, ld_st, st_dtype, n_groups;
+    int32_t M, y_dtype, k_steps, k_per_split;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));   // first source -> upper half
+    return r;
+}
+
+// D[tmem] (+)= A[tmem] * B[smem], bf16 x bf16 -> fp32, issued by ONE thread.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 registers per thread -> 32 consecutive columns of this thread's TMEM lane (whole warp).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x, const Args a) {
+    constexpr int B_BYTES = BN * KS * 2;                 // two [BN x 64] bf16 sub-tiles
+    constexpr int STAGE_BYTES = IDX_BYTES + B_BYTES;     // multiple of 1024
+    extern __shared__ __align__(1024) char smem_raw[];
+    const uint32_t smem_base = sm100::smem_u32(smem_raw);
+    const uint32_t lut_base = (smem_base + 0xFFFFu) & ~0xFFFFu;
+    // stages: as many as fit below the table, the rest above it
+    const uint32_t lo0 = (smem_base + 1023u) & ~1023u;
+    const uint32_t hi0 = lut_base + LUT_BYTES;
+    const int n_lo = (int)((lut_base - lo0) / STAGE_BYTES);
+    const int n_hi = (int)((smem_base + SMEM_TOTAL - hi0) / STAGE_BYTES);
+    const int STAGES = (n_lo + n_hi) < MAX_STAGES ? (n_lo + n_hi) : MAX_STAGES;
+    auto stage_ptr = [&](int s) -> char* {
+        const uint32_t addr = s < n_lo ? lo0 + (uint32_t)s * STAGE_BYTES : hi0 + (uint32_t)(s - n_lo) * STAGE_BYTES;
+        return smem_raw + (addr - smem_base);
+    };
+    char* lut = smem_raw + (lut_base - smem_base);
+    // barriers live in the unused upper half of the table's first row
+    uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 128);
+    uint64_t* tma_full = bars;                       // [MAX_STAGES] index + activation bytes landed
+    uint64_t* a_full = bars + MAX_STAGES;            // [MAX_STAGES] A columns of the stage written
+    uint64_t* empty = bars + 2 * MAX_STAGES;         // [MAX_STAGES] MMAs of the stage retired
+    uint64_t* acc_full = bars + 3 * MAX_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * MAX_STAGES + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BN;
+    const int o0 = blockIdx.y * BM;
+    const int KS0 = blockIdx.z * a.k_per_split;
+    const int NK = (a.k_steps - KS0 < a.k_per_split) ? a.k_steps - KS0 : a.k_per_split;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
+            sm100::mbar_init(&tma_full[s], 1);
+            sm100::mbar_init(&a_full[s], DEQ_WARPS);
+            sm100::mbar_init(&empty[s], 1);
+        }
+        sm100::mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        sm100::fence_barrier_init();
+        sm100::prefetch_tensormap(&map_idx);
+        sm100::prefetch_tensormap(&map_x);
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc(tmem_slot, TMEM_COLS);
+        sm100::tmem_relinquish();
+    }
+    // lane-replicated codebook (the lower 128 bytes of each 256-byte row)
+    for (int i = threadIdx.x; i < 256 * 32; i += NUM_THREADS)
+        *reinterpret_cast<float*>(lut + (i >> 5) * 256 + (i & 31) * 4) = a.cb[i >> 5];
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a0 = tmem_base + (uint32_t)BN;       // A stages follow the accumulator's BN columns
+
+    if (STAGES < 2) {   // cannot happen with the sizes above; never run a pipeline that cannot make progress
+        if (threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, HXQ_E_SHAPE);
+    } else if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int armed = 0;
+            for (int ks = 0; ks < NK; ++ks) {
+                const int s = ks % STAGES;
+                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+                if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+                char* st = stage_ptr(s);
+                sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)STAGE_BYTES);
+                sm100::tma_load_2d(st, &map_idx, &tma_full[s], (KS0 + ks) * KS, o0);
+                sm100::tma_load_2d(st + IDX_BYTES, &map_x, &tma_full[s], (KS0 + ks) * KS, m0);
+                sm100::tma_load_2d(st + IDX_BYTES + BN * 128, &map_x, &tma_full[s], (KS0 + ks) * KS + 64, m0);
+                armed = ks + 1;
+            }
+            if (*abort_flag != 0) {
+                for (int ks = (armed > STAGES ? armed - STAGES : 0); ks < armed; ++ks)
+                    sm100::mbar_wait(&tma_full[ks % STAGES], (uint32_t)(ks / STAGES) & 1u, abort_flag, 200000000LL);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = sm100::make_idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int ks = 0; ks < NK && ok; ++ks) {
+                const int s = ks % STAGES;
+                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+                ok = sm100::mbar_wait(&tma_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
+                if (!ok) break;
+                sm100::tc_fence_after_sync();
+                char* st = stage_ptr(s);
+#pragma unroll
+                for (int kk = 0; kk < KS / 16; ++kk) {
+                    // B: sub-tile kk / 4 (64 K columns each), + 32 bytes per 16-column slice inside it
+                    const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(st + IDX_BYTES + (kk >> 2) * (BN * 128))) +
+                                        (uint64_t)(2 * (kk & 3));
+                    umma_bf16_ts(tmem_base, tmem_a0 + (uint32_t)(s * A_COLS + kk * 8), db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                }
+                sm100::umma_commit(&empty[s]);
+            }
+            if (ok) sm100::umma_commit(acc_full);
+        }
+    } else {
+        // ------------------------------------------------------------ dequantising warps
+        const int dw = warp - 2;
+        const int quarter = warp & 3;                 // TMEM lanes this warp may touch: [32 * quarter, +32)
+        const int khalf = (dw >> 2) & 1;              // which 64 columns of each stage
+        // warps 2..9: warp & 3 takes the values 2,3,0,1,2,3,0,1: every quarter gets exactly two warps, dw>>2 = 0 and 1
+        const int r = 32 * quarter + lane;            // row inside the CTA tile == TMEM lane
+        const int row = o0 + r;
+        const bool row_ok = row < a.out_features;
+        const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
+        const bool affine = a.group_size > 0;
+        const int g_base = affine ? a.col0 / a.group_size : 0;
+        const uint32_t t_row = tmem_a0 + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(khalf * 32);
+
+        auto load_st = [&](int ks, float& s, float& t) {
+            s = 1.f; t = 0.f;
+            if (affine && row_ok) {
+                int g = (a.col0 + (KS0 + ks) * KS + khalf * 64) / a.group_size - g_base;
+                g = g < a.n_groups ? g : a.n_groups - 1;      // K tail: those activations are zero
+                const int64_t o = (int64_t)row * a.ld_st + g;
+                if (a.st_dtype == HXQ_F32) {
+                    s = reinterpret_cast<const float*>(a.scales)[o];
+                    t = reinterpret_cast<const float*>(a.offsets)[o];
+                } else {
+                    s = __half2float(reinterpret_cast<const __half*>(a.scales)[o]);
+                    t = __half2float(reinterpret_cast<const __half*>(a.offsets)[o]);
+                }
+            }
+        };
+        float sc_n, of_n;
+        load_st(0, sc_n, of_n);
+        for (int ks = 0; ks < NK; ++ks) {
+            const int s = ks % STAGES;
+            const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+            const float sc = sc_n, of = of_n;
+            if (ks + 1 < NK) load_st(ks + 1, sc_n, of_n);
+            if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
+            const uint32_t idx_row = sm100::smem_u32(stage_ptr(s)) + (uint32_t)(r * 128);
+            uint32_t out[32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {     // 16 codes per load: chunk 4 * khalf + c of the row, swizzled by the row
+                const uint32_t addr = idx_row + ((uint32_t)((4 * khalf + c) ^ (r & 7)) << 4);
+                uint32_t w[4];
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const uint32_t a0 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)((j & 3) << 4));
+                    const uint32_t a1 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)(((j + 1) & 3) << 4));
+                    float v0, v1;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v0) : "r"(a0));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v1) : "r"(a1));
+                    out[c * 8 + (j >> 1)] = pack_bf16x2(fmaf(v0, sc, of), fmaf(v1, sc, of));
+                }
+            }
+            tmem_st_32x32(t_row + (uint32_t)(s * A_COLS), out);
+            tmem_st_wait();
+            sm100::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) sm100::mbar_arrive(&a_full[s]);
+        }
+
+        // ------------------------------------------------------------ epilogue
+        // warps of one quarter split the token columns: dw >> 2 == 0 takes the first half
+        {
+            constexpr int COLS_PER_WARP = BN / 2;        // 16, 32 or 64
+            const int c_lo = khalf * COLS_PER_WARP;
+            if (sm100::mbar_wait(acc_full, 0u, abort_flag)) {
+                sm100::tc_fence_after_sync();
+                float* part = a.partial ? a.partial + (int64_t)blockIdx.z * a.M * a.out_features : nullptr;
+                const float bias = (a.bias != nullptr && row_ok && part == nullptr) ? a.bias[row] : 0.f;
+                // this row's sidecar entries inside this CTA's K range
+                int e0 = 0, e1 = 0;
+                if (a.rowptr != nullptr && row_ok) {
+                    e0 = a.rowptr[row];
+                    e1 = a.rowptr[row + 1];
+                    const int k_lo = KS0 * KS, k_hi = (KS0 + NK) * KS;
+                    while (e0 < e1 && a.cols[e0] < k_lo) ++e0;
+                    while (e1 > e0 && a.cols[e1 - 1] >= k_hi) --e1;
+                }
+#pragma unroll 1
+                for (int c0 = c_lo; c0 < c_lo + COLS_PER_WARP; c0 += 16) {
+                    if (m0 + c0 >= a.M) break;           // warp-uniform
+                    uint32_t v[16];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        : "r"(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0)
+                        : "memory");
+                    sm100::tmem_ld_wait();
+                    float acc[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
+                    for (int e = e0; e < e1; ++e) {
+                        const int c = a.cols[e];
+                        const float dl = a.deltas[e];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = m0 + c0 + j;
+                            if (m < a.M) acc[j] = fmaf(dl, __bfloat162float(a.xb[(int64_t)m * a.ldxb + c]), acc[j]);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + c0 + j;
+                        if (row_ok && m < a.M) {
+                            if (part != nullptr) part[(int64_t)m * a.out_features + row] = acc[j];
+                            else store_from_f32(a.y, (int64_t)m * a.ldy + row, acc[j] + bias, a.y_dtype);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        sm100::tc_fence_after_sync();
+        sm100::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0 && a.status != nullptr) atomicExch(a.status, HXQ_E_TIMEOUT);
+}
+
+// ---- host side ---------------------------------------------------------------------
+
+static int sm_count() {
+    int n_sm = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        n_sm <= 0)
+        n_sm = 148;
+    return n_sm;
+}
+
+static int pick_bn(int M) { return M > 64 ? 128 : (M > 32 ? 64 : 32); }
+
+// K slices per output tile: enough CTAs to fill the GPU when the row-tile grid alone does not, at
+// least four stages each.
+static int pick_splits(int grid_m, int grid_o, int k_steps, int n_sm) {
+    const int tiles = grid_m * grid_o;
+    if (tiles * 2 > n_sm) return 1;
+    int s = n_sm / tiles;
+    if (s > 8) s = 8;
+    if (s > k_steps / 4) s = k_steps / 4;
+    return s < 1 ? 1 : s;
+}
+
+// Largest token count this kernel takes (128); HXQ_GEMM_TS_MAX_M lowers it (0 = never) for A/B timing.
+static int max_tokens() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("HXQ_GEMM_TS_MAX_M");
+        int n = e ? atoi(e) : 128;
+        v = n < 0 ? 0 : (n > 128 ? 128 : n);
+    }
+    return v;
+}
+
+bool covers(const hxq_desc* d, int32_t M) {
+    return M >= 1 && M <= max_tokens() && (d->in_features % 16 == 0) && (d->ld_idx % 16 == 0) && aligned_to(d->indices, 16) &&
+           (d->col0 % 64 == 0) && (d->group_size == 0 || d->group_size % 64 == 0);
+}
+
+size_t split_bytes(const hxq_desc* d, int32_t M) {
+    const int BN = pick_bn(M);
+    const int s = pick_splits((M + BN - 1) / BN, (d->out_features + BM - 1) / BM, (d->in_features + KS - 1) / KS, sm_count());
+    return s > 1 ? (size_t)s * M * d->out_features * sizeof(float) : 0;
+}
+
+template <int BN>
+static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, int grid_m, int grid_o, int splits,
+                  cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemm_ts_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess)
+            return HXQ_E_DEVICE;
+        attr_set[dev] = true;
+    }
+    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mi, mx, a);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+// xb: the activations as bf16 with a 16-byte aligned row stride (the caller converted them if needed);
+// split_ws: room for the fp32 partials (split_bytes) or nullptr.
+int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, void* y, int y_dtype, int64_t ldy,
+        void* split_ws, size_t split_ws_bytes, int32_t* status_word, cudaStream_t stream) {
+    const int BN = pick_bn(M);
+    CUtensorMap mi, mx;
+    if (!gemm::make_map_2d(&mi, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->indices, (uint64_t)d->in_features,
+                           (uint64_t)d->out_features, (uint64_t)d->ld_idx, KS, BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return HXQ_E_DEVICE;
+    if (!gemm::make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, (uint64_t)d->in_features, (uint64_t)M,
+                           (uint64_t)ldxb * 2, 64, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return HXQ_E_DEVICE;
+    Args a;
+    a.cb = d->codebook; a.scales = d->scales; a.offsets = d->offsets;
+    a.rowptr = d->rowptr; a.cols = d->cols; a.deltas = d->deltas; a.bias = d->bias;
+    a.xb = xb; a.ldxb = ldxb;
+    a.y = y; a.status = status_word; a.ldy = ldy;
+    a.out_features = d->out_features; a.in_features = d->in_features; a.col0 = d->col0;
+    a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
+    a.n_groups = d->group_size > 0 ? (d->col0 + d->in_features - 1) / d->group_size - d->col0 / d->group_size + 1 : 0;
+    a.M = M; a.y_dtype = y_dtype;
+    a.k_steps = (d->in_features + KS - 1) / KS;
+    const int grid_o = (d->out_features + BM - 1) / BM;
+    const int grid_m = (M + BN - 1) / BN;
+    int splits = pick_splits(grid_m, grid_o, a.k_steps, sm_count());
+    a.k_per_split = a.k_steps;
+    a.partial = nullptr;
+    if (splits > 1 && split_ws && aligned_to(split_ws, 16) &&
+        split_ws_bytes >= (size_t)splits * M * d->out_features * sizeof(float)) {
+        a.k_per_split = (a.k_steps + splits - 1) / splits;
+        splits = (a.k_steps + a.k_per_split - 1) / a.k_per_split;   // no empty slice
+        a.partial = reinterpret_cast<float*>(split_ws);
+    } else {
+        splits = 1;
+    }
+    int st;
+    if (BN == 128) st = launch<128>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 64) st = launch<64>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else st = launch<32>(mi, mx, a, grid_m, grid_o, splits, stream);
+    if (st != HXQ_OK || splits == 1) return st;
+    gemm::launch_splitk_reduce(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy, stream);
+    return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+}  // namespace gemmts
+}  // namespace hxq

@@ -540,7 +540,40 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t w, uint64_t x) {
     return r;
 }
 
-template <int MP>
+// 16 activations of this lane (columns col .. col+15 of the token row at xrow) as 8 packed fp32 pairs
+template <int XDT>
+__device__ __forceinline__ void x_lane16(const void* xrow, int col, uint64_t (&xp)[8]) {
+    if (XDT == HXQ_F32) {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(xrow) + col);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 v = p[j];
+            xp[2 * j] = pack2(v.x, v.y);
+            xp[2 * j + 1] = pack2(v.z, v.w);
+        }
+    } else {
+        const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(xrow) + col);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint4 v = p[j];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float lo, hi;
+                if (XDT == HXQ_BF16) {
+                    lo = __uint_as_float(w[q] << 16);
+                    hi = __uint_as_float(w[q] & 0xffff0000u);
+                } else {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[q]);
+                    lo = __low2float(h); hi = __high2float(h);
+                }
+                xp[4 * j + q] = pack2(lo, hi);
+            }
+        }
+    }
+}
+
+template <int MP, int XDT, int STM, bool SIDE>
 __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1)
 gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     extern __shared__ __align__(1024) char dyn_smem[];
@@ -555,7 +588,7 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     float* part_s = reinterpret_cast<float*>(lut + kLutBytes);   // [unit - S0][RM]
     // staging: 2 W unit buffers of 4 KB (warp w owns 2w and 2w+1), as many as fit below the table and
     // the rest above the slots, then one activation chunk per warp
-    const int xs_lane = (a.x_dtype == HXQ_F32) ? 64 : 32;          // bytes of one token's 16 activations
+    constexpr int xs_lane = (XDT == HXQ_F32) ? 64 : 32;          // bytes of one token's 16 activations
     uint32_t ring_q0, ring_q1, ring_x;
     {
         constexpr uint32_t kUnitBytes = kRows * kChunk;
@@ -590,9 +623,11 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     const int S0 = rb_first * nch;           // first unit of the first row block this CTA touches
     const int r_l = lane & 7;
     const int h_l = lane >> 3;
-    const bool affine = a.group_size > 0;
-    const bool st_f32 = a.st_dtype == HXQ_F32;
-    const bool sidecar = a.rowptr != nullptr;
+    constexpr bool affine = STM != 0;
+    constexpr bool st_f32 = STM == 1;
+    const int M = a.M;
+    const int64_t ldx = a.ldx;
+    const char* const xbase = reinterpret_cast<const char*>(a.x);
     const uint32_t ld = (uint32_t)a.ld_idx;
     const int d_rb = W / nch, d_ch = W - d_rb * nch;
     // sidecar carriers of row block rb: the units with (chunk - rb) mod nch < n_car
@@ -618,15 +653,15 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
         __syncwarp();
         if (lane == 0 && alive) {
             const uint32_t bar = bar0 + buf * 8;
-            const uint32_t xbytes = with_x ? (uint32_t)(a.M * 32 * xs_lane) : 0u;
+            const uint32_t xbytes = with_x ? (uint32_t)(M * 32 * xs_lane) : 0u;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"((uint32_t)(kRows * kChunk) + xbytes) : "memory");
             asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                          :: "r"(buf ? ring_q1 : ring_q0), "l"(reinterpret_cast<uint64_t>(&tmap)), "r"(bar), "r"(ch * (kChunk / 4)), "r"(rb * kRows) : "memory");
             if (with_x) {
-                const char* xg = reinterpret_cast<const char*>(a.x) + (size_t)(ch * kChunk) * (xs_lane >> 4);
-                for (int m = 0; m < a.M; ++m)
+                const char* xg = xbase + (size_t)(ch * kChunk) * (xs_lane >> 4);
+                for (int m = 0; m < M; ++m)
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 :: "r"(ring_x + m * 32 * xs_lane), "l"(xg + (size_t)m * a.ldx * (xs_lane >> 4)), "r"(32 * xs_lane), "r"(bar) : "memory");
+                                 :: "r"(ring_x + m * 32 * xs_lane), "l"(xg + (size_t)m * ldx * (xs_lane >> 4)), "r"(32 * xs_lane), "r"(bar) : "memory");
             }
         }
 #else
@@ -635,11 +670,11 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
                          :: "r"((buf ? ring_q1 : ring_q0) + r * kChunk), "l"(p + (uint64_t)ld * (uint32_t)r) : "memory");
         if (with_x) {   // warp-uniform: the unit's chunk differs from the one whose activations are in registers
-            const char* xg = reinterpret_cast<const char*>(a.x) + (size_t)(ch * kChunk + lane * 16) * (xs_lane >> 4);
+            const char* xg = xbase + (size_t)(ch * kChunk + lane * 16) * (xs_lane >> 4);
 #pragma unroll
             for (int m = 0; m < MP; ++m) {
-                if (m < a.M) {
-                    const char* xm = xg + (size_t)m * a.ldx * (xs_lane >> 4);
+                if (m < M) {
+                    const char* xm = xg + (size_t)m * ldx * (xs_lane >> 4);
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane), "l"(xm) : "memory");
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(ring_x + m * 32 * xs_lane + kXPiece), "l"(xm + 16) : "memory");
                     if (xs_lane == 64) {
@@ -661,7 +696,7 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
             }
         }
         f.e = 0; f.e1 = 0; f.last = false;
-        if (sidecar) {
+        if (SIDE) {
             int i = ch - own;
             if (i < 0) i += nch;
             if (i < n_car) {   // entry 4 i + (lane >> 3) of row lane & 7
@@ -700,14 +735,24 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     };
     auto load_x = [&](int c) {          // straight from global: the first unit only
         float xr[MP][16];
-        load_x_chunk<MP>(a, c * kChunk + lane * 16, true, xr);
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            uint64_t t8[8];
+            if (m < M) x_lane16<XDT>(xbase + (size_t)m * ldx * (XDT == HXQ_F32 ? 4 : 2), c * kChunk + lane * 16, t8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float lo = 0.f, hi = 0.f;
+                if (m < M) asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(t8[j]));
+                xr[m][2 * j] = lo; xr[m][2 * j + 1] = hi;
+            }
+        }
         set_x(xr, c);
     };
     auto read_x = [&](int c) {          // from the copy a fetch left in shared memory
         float xr[MP][16];
 #pragma unroll
         for (int m = 0; m < MP; ++m) {
-            if (m >= a.M) {
+            if (m >= M) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) xr[m][j] = 0.f;
                 continue;
@@ -720,10 +765,10 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
                                  : "=r"(w[4 * k]), "=r"(w[4 * k + 1]), "=r"(w[4 * k + 2]), "=r"(w[4 * k + 3])
                                  : "r"(ring_x + m * 32 * xs_lane + kXPiece * k));
             }
-            if (a.x_dtype == HXQ_F32) {
+            if (XDT == HXQ_F32) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) xr[m][j] = __uint_as_float(w[j]);
-            } else if (a.x_dtype == HXQ_BF16) {
+            } else if (XDT == HXQ_BF16) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) { xr[m][2 * j] = __uint_as_float(w[j] << 16); xr[m][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
             } else {
@@ -769,10 +814,12 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     auto compute = [&](const LeanFetch& f, int buf, int pu) {
         // this lane's sidecar entry: column and delta go out now, the activation it meets after the
         // first half of the lookups, the product at the end
-        const bool sc = f.e < f.e1;
+        bool sc = false;
         int sc_c = 0;
         float sc_d = 0.f, sc_x[MP];
-        if (sc) { sc_c = a.cols[f.e]; sc_d = a.deltas[f.e]; }
+        if (SIDE) { sc = f.e < f.e1; if (sc) { sc_c = a.cols[f.e]; sc_d = a.deltas[f.e]; } }
+#pragma unroll
+        for (int m = 0; m < MP; ++m) sc_x[m] = 0.f;
         float acc[kRows * MP];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -813,10 +860,10 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
             for (int r = 0; r < 4; ++r)
 #pragma unroll
                 for (int m = 0; m < MP; ++m) acc[(4 * half + r) * MP + m] = sum2(p2[r][m]);
-            if (half == 0) {
+            if (SIDE && half == 0) {
 #pragma unroll
                 for (int m = 0; m < MP; ++m)
-                    sc_x[m] = (sc && m < a.M) ? load_as_f32(a.x, (int64_t)m * a.ldx + sc_c, a.x_dtype) : 0.f;
+                    sc_x[m] = (sc && m < M) ? Elem<XDT>::load(xbase, (int64_t)m * ldx + sc_c) : 0.f;
             }
         }
         halve<kRows * MP>(acc, lane, 4);
@@ -826,15 +873,17 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
 #pragma unroll
             for (int m = 0; m < MP; ++m) acc[m] = fmaf(f.s, acc[m], f.t * xsum[m]);
         }
+        if (SIDE) {
 #pragma unroll
-        for (int m = 0; m < MP; ++m) acc[m] = fmaf(sc_d, sc_x[m], acc[m]);
-        if (f.last) {   // rows with more entries than the carriers take in one go
+            for (int m = 0; m < MP; ++m) acc[m] = fmaf(sc_d, sc_x[m], acc[m]);
+        }
+        if (SIDE && f.last) {   // rows with more entries than the carriers take in one go
             for (int e = f.e + 4; e < f.e1; e += 4) {
                 const int c = a.cols[e];
                 const float dl = a.deltas[e];
 #pragma unroll
                 for (int m = 0; m < MP; ++m)
-                    if (m < a.M) acc[m] = fmaf(dl, load_as_f32(a.x, (int64_t)m * a.ldx + c, a.x_dtype), acc[m]);
+                    if (m < M) acc[m] = fmaf(dl, Elem<XDT>::load(xbase, (int64_t)m * ldx + c), acc[m]);
             }
         }
         int m_i = 0;
@@ -1120,31 +1169,69 @@ static bool gemv_lean_shape(const hxq_desc* d, const GemvPlan& p, bool x_vec) {
     return (int64_t)d->out_features * (d->group_size ? d->ld_st : 0) <= 0x7fffffffLL;
 }
 
+static cudaLaunchConfig_t gemv_launch_config(const GemvPlan& p, int smem_bytes, cudaStream_t stream, cudaLaunchAttribute* attr) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(p.warps_per_cta * 32);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up may overlap the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
+
 template <int MP>
-static int launch_fast(const GemvArgs& a, const GemvPlan& p, const CUtensorMap* tmap, cudaStream_t stream) {
-    const bool lean = tmap != nullptr;
+static int launch_edge(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(gemv_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes) != cudaSuccess)
             return HXQ_E_DEVICE;
-        if (cudaFuncSetAttribute(gemv_lean_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLeanSmemBytes) != cudaSuccess)
+        attr_set[dev] = true;
+    }
+    cudaLaunchAttribute attr[1];
+    const cudaLaunchConfig_t cfg = gemv_launch_config(p, kGemvSmemBytes, stream, attr);
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a) == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+// The lean kernel is compiled once per (tokens per launch, activation type, scale/offset type, sidecar):
+// none of those is looked at inside the unit loop.
+template <int MP, int XDT, int STM, bool SIDE>
+static int launch_lean_one(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kern = gemv_lean_kernel<MP, XDT, STM, SIDE>;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kLeanSmemBytes) != cudaSuccess)
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.grid);
-    cfg.blockDim = dim3(p.warps_per_cta * 32);
-    cfg.dynamicSmemBytes = lean ? kLeanSmemBytes : kGemvSmemBytes;
-    cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up may overlap the previous kernel's tail
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const cudaError_t e = lean ? cudaLaunchKernelEx(&cfg, gemv_lean_kernel<MP>, *tmap, a) : cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a);
-    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+    const cudaLaunchConfig_t cfg = gemv_launch_config(p, kLeanSmemBytes, stream, attr);
+    return cudaLaunchKernelEx(&cfg, kern, tmap, a) == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+template <int MP, int XDT>
+static int launch_lean_st(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
+    const int stm = a.group_size > 0 ? (a.st_dtype == HXQ_F32 ? 1 : 2) : 0;
+    const bool side = a.rowptr != nullptr;
+    if (stm == 0) return side ? launch_lean_one<MP, XDT, 0, true>(a, p, tmap, stream) : launch_lean_one<MP, XDT, 0, false>(a, p, tmap, stream);
+    if (stm == 1) return side ? launch_lean_one<MP, XDT, 1, true>(a, p, tmap, stream) : launch_lean_one<MP, XDT, 1, false>(a, p, tmap, stream);
+    return side ? launch_lean_one<MP, XDT, 2, true>(a, p, tmap, stream) : launch_lean_one<MP, XDT, 2, false>(a, p, tmap, stream);
+}
+template <int MP>
+static int launch_lean(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
+    if (a.x_dtype == HXQ_F32) return launch_lean_st<MP, HXQ_F32>(a, p, tmap, stream);
+    if (a.x_dtype == HXQ_F16) return launch_lean_st<MP, HXQ_F16>(a, p, tmap, stream);
+    return launch_lean_st<MP, HXQ_BF16>(a, p, tmap, stream);
+}
+
+template <int MP>
+static int launch_fast(const GemvArgs& a, const GemvPlan& p, const CUtensorMap* tmap, cudaStream_t stream) {
+    return tmap != nullptr ? launch_lean<MP>(a, p, *tmap, stream) : launch_edge<MP>(a, p, stream);
 }
 
 // Shared by hxq_gemv and (until M is large enough for the tensor-core kernel)

@@ -391,6 +391,105 @@ class Qwen2HxqDecoder(nn.Module):
         return torch.stack(outs, 1)
 
 
+def run_decode(shape: str, batches, prompt: int, new_tokens: int, device, rank: int = 0, world: int = 1, *,
+               layers: int = 0, build: str = "local", allreduce: str = "p2p", fuse_proj: bool = True,
+               graph: bool = True, torch_glue: bool = False, fill_cache: bool = False):
+    """Build ONE random-init HXQ decoder of the named shape and, for every batch size in ``batches``,
+    prefill ``prompt`` tokens per sequence and time ``new_tokens - 1`` greedy steps (CUDA events, max
+    over ranks).  ``fill_cache`` replaces the prefill by random K/V rows (decode speed at a given
+    context without paying for the prompt).  Returns one dict of measurements per batch size (every
+    rank gets the same numbers)."""
+    import gc
+    import time
+    batches = [int(b) for b in ([batches] if isinstance(batches, int) else batches)]
+    shp = {"7b": Qwen2Shape.qwen25_7b, "14b": Qwen2Shape.qwen25_14b, "tiny": Qwen2Shape.tiny}[shape]()
+    if layers:
+        shp.layers = layers
+    t0 = time.perf_counter()
+    model = Qwen2HxqDecoder(shp, device, max(batches), prompt + new_tokens + 8, rank=rank, world=world,
+                            fuse_proj=fuse_proj, p2p_allreduce=(allreduce == "p2p"), build=build)
+    torch.cuda.synchronize(device)
+    build_s = time.perf_counter() - t0
+    k_full, v_full = model.k_cache, model.v_cache
+    hxq_mods = [m for m in model.modules() if isinstance(m, HelixLinear)]
+    out = []
+    for batch in batches:
+        model.k_cache, model.v_cache = k_full[:, :batch], v_full[:, :batch]
+        for name in ("_graph", "_sb"):
+            if hasattr(model, name):
+                delattr(model, name)
+        ids = torch.randint(0, shp.vocab, (batch, prompt), device=device,
+                            generator=torch.Generator(device=device).manual_seed(0))
+        prefill_ms = None
+        with torch.no_grad():
+            if fill_cache:
+                g = torch.Generator(device=device).manual_seed(1 + rank)
+                for li in range(shp.layers):   # layer by layer: the fp32 temporaries stay small
+                    for cache in (model.k_cache, model.v_cache):
+                        view = cache[li][:, :, :prompt]
+                        view.copy_(torch.randn(view.shape, device=device, generator=g) * 0.5)
+                nxt = ids[:, -1].clone()
+            else:
+                model.prefill(ids[:, : min(prompt, 64)])            # warm-up call (first-use set-up of every kernel)
+                torch.cuda.synchronize(device)
+                p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                p0.record()
+                nxt = model.prefill(ids)
+                p1.record()
+                torch.cuda.synchronize(device)
+                prefill_ms = p0.elapsed_time(p1)
+            run = None
+            if graph:
+                run, tok, pos = model.make_graphed_step(batch, fused=not torch_glue)
+            torch.cuda.synchronize(device)
+            e1, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e1.record()
+            for i in range(new_tokens - 1):
+                p = prompt + i
+                if run is not None:
+                    tok.copy_(nxt[:, None])
+                    pos.fill_(p)
+                    nxt = run()
+                else:
+                    pt = torch.tensor([p], device=device)
+                    if torch_glue:
+                        nxt = model.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
+                    else:
+                        nxt = model.step_fused(nxt[:, None], pt).argmax(-1)
+            e2.record()
+            torch.cuda.synchronize(device)
+        ms_dec = e1.elapsed_time(e2) / max(1, new_tokens - 1)
+        t = torch.tensor([ms_dec, prefill_ms or 0.0], device=device, dtype=torch.float64)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_dec, pf = float(t[0].item()), float(t[1].item())
+        hxq_bytes = sum(m.packed().algorithmic_bytes(batch, 2, 2) for m in hxq_mods)
+        ar_status = None
+        if world > 1 and getattr(model, "_ar", None) is not None:
+            ar_status = model._ar.check_status()
+        out.append({
+            "tok_s": batch * 1000.0 / ms_dec, "ms_per_step": ms_dec, "batch": batch, "context": prompt,
+            "new_tokens": new_tokens, "shape": shape, "layers": shp.layers, "n_gpus": world,
+            "launch": "python" if run is None else "cuda_graph", "glue": "torch" if torch_glue else "fused",
+            "projections": "qkv,o,gate_up,down" if fuse_proj else "q,k,v,o,gate,up,down",
+            "allreduce": (allreduce if world > 1 else None), "allreduce_status": ar_status,
+            "weights": f"random N(0, 0.02), compressed per {'full matrix then sharded' if build == 'global' else 'shard'}",
+            "hxq_bytes_per_step_per_gpu": hxq_bytes, "hxq_GBps_per_gpu": hxq_bytes / (ms_dec * 1e-3) / 1e9,
+            "prefill_ms": (pf if prefill_ms is not None else None),
+            "prefill_tok_s": (batch * prompt / (pf * 1e-3) if prefill_ms is not None else None),
+            "kv_cache": "random rows (no prefill)" if fill_cache else "from the prefill",
+            "tokens_valid": bool(int(nxt.min()) >= 0 and int(nxt.max()) < shp.vocab), "build_s": build_s,
+        })
+        run = None
+    for name in ("_graph", "_ar", "_sb"):
+        if hasattr(model, name):
+            delattr(model, name)
+    del model, k_full, v_full, hxq_mods
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
 def main(argv=None):
     """``python -m helix_substrate_b200.qwen2_decode --shape 7b --batch 1 --prompt 2048 --new 128``
     (under torchrun for tensor parallel).  Prints one JSON line with decode
@@ -398,7 +497,6 @@ def main(argv=None):
     import argparse
     import json
     import os
-    import time
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="7b", choices=["7b", "14b", "tiny"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the shape's own)")
@@ -411,6 +509,7 @@ def main(argv=None):
                     help="tensor-parallel sum in the fused step: NCCL, or the one-shot peer-memory kernel")
     ap.add_argument("--build", default="local", choices=["local", "global"],
                     help="local: each rank compresses matrices of its shard's shape; global: full matrices, then sharded")
+    ap.add_argument("--fill-cache", action="store_true", help="random K/V rows instead of a prefill")
     ap.add_argument("--separate-proj", action="store_true",
                     help="q, k, v and gate, up as separate compressed matrices (7 products per layer instead of 4)")
     args = ap.parse_args(argv)
@@ -419,70 +518,26 @@ def main(argv=None):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # plain peer-to-peer only: no buffer of this process is ever bound to an NVLink multicast
-        # object (a rank that goes away while bound to one takes its peers' GPUs with it)
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        torch.distributed.init_process_group("nccl", device_id=dev)
-    shp = {"7b": Qwen2Shape.qwen25_7b, "14b": Qwen2Shape.qwen25_14b, "tiny": Qwen2Shape.tiny}[args.shape]()
-    if args.layers:
-        shp.layers = args.layers
-    t0 = time.perf_counter()
-    model = Qwen2HxqDecoder(shp, dev, args.batch, args.prompt + args.new + 8, rank=rank, world=world,
-                            fuse_proj=not args.separate_proj, p2p_allreduce=args.allreduce == "p2p", build=args.build)
-    torch.cuda.synchronize()
-    build_s = time.perf_counter() - t0
-    prompt = torch.randint(0, shp.vocab, (args.batch, args.prompt), device=dev,
-                           generator=torch.Generator(device=dev).manual_seed(0))
-    with torch.no_grad():
-        p0, p1, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
-        p0.record()
-        nxt = model.prefill(prompt)
-        p1.record()
-        if args.no_graph:
-            run = None
-        else:
-            run, tok, pos = model.make_graphed_step(args.batch, fused=not args.torch_glue)
-        torch.cuda.synchronize()
-        # timed decode: new-1 graph replays
-        e1.record()
-        for i in range(args.new - 1):
-            p = args.prompt + i
-            if run is not None:
-                tok.copy_(nxt[:, None])
-                pos.fill_(p)
-                nxt = run()
-            else:
-                pt = torch.tensor([p], device=dev)
-                if args.torch_glue:
-                    nxt = model.forward_tokens(nxt[:, None], pt, pt, None).argmax(-1)
-                else:
-                    nxt = model.step_fused(nxt[:, None], pt).argmax(-1)
-        e2.record()
-        torch.cuda.synchronize()
-    ms_dec = e1.elapsed_time(e2) / (args.new - 1)
-    t = torch.tensor([ms_dec], device=dev, dtype=torch.float64)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms_dec = float(t.item())
-    hxq_bytes = sum(m.packed().algorithmic_bytes(args.batch, 2, 2) for m in model.modules()
-                    if isinstance(m, HelixLinear))
+        init_tensor_parallel(dev)
+    res = run_decode(args.shape, [args.batch], args.prompt, args.new, dev, rank, world, layers=args.layers,
+                     build=args.build, allreduce=args.allreduce, fuse_proj=not args.separate_proj,
+                     graph=not args.no_graph, torch_glue=args.torch_glue, fill_cache=args.fill_cache)[0]
     if rank == 0:
-        print(json.dumps({
-            "metric": "decode_tokens_per_s", "value": args.batch * 1000.0 / ms_dec, "unit": "tok/s",
-            "ms_per_token_step": ms_dec, "batch": args.batch, "prompt": args.prompt, "new_tokens": args.new,
-            "shape": args.shape, "layers": shp.layers, "n_gpus": world, "launch": "python" if run is None else "cuda_graph",
-            "glue": "torch" if args.torch_glue else "fused",
-            "projections": "q,k,v,o,gate,up,down" if args.separate_proj else "qkv,o,gate_up,down",
-            "allreduce": (args.allreduce if world > 1 else None),
-            "hxq_algorithmic_bytes_per_step_per_gpu": hxq_bytes,
-            "hxq_GBps_per_gpu_if_all_time_were_linears": hxq_bytes / (ms_dec * 1e-3) / 1e9,
-            "prefill_ms": p0.elapsed_time(p1), "build_s": build_s,
-            "data": "synthetic: N(0,0.02) weights, uniform random prompt ids",
-        }), flush=True)
+        print(json.dumps({"metric": "decode_tokens_per_s", "value": res["tok_s"], "unit": "tok/s", **res,
+                          "data": "synthetic: N(0,0.02) weights, uniform random prompt ids"}), flush=True)
     if world > 1:
-        leave_process_group(model)
+        leave_process_group()
+
+
+def init_tensor_parallel(device) -> None:
+    """NCCL process group for one node, plain peer-to-peer only: no buffer of this process is ever
+    bound to an NVLink multicast object (a rank that goes away while bound to one takes its peers'
+    GPUs down with it), neither by NCCL (NVLS off) nor by symmetric memory."""
+    import os
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    torch.distributed.init_process_group("nccl", device_id=device)
 
 
 def leave_process_group(*holders) -> None:
