@@ -70,6 +70,10 @@ def lib() -> C.CDLL:
     L.hxq_gemv.restype = C.c_int
     L.hxq_gemv.argtypes = [P, C.c_void_p, C.c_int, C.c_int32, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
                            C.c_void_p, C.c_size_t, C.c_void_p]
+    L.hxq_gemv_packed6.restype = C.c_int
+    L.hxq_gemv_packed6.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int, C.c_int32,
+                                   C.c_int32, C.c_void_p, C.c_void_p, C.c_int, C.c_int32, C.c_int64, C.c_void_p,
+                                   C.c_int, C.c_int64, C.c_void_p]
     L.hxq_gemm_workspace_bytes.restype = C.c_size_t
     L.hxq_gemm_workspace_bytes.argtypes = [P, C.c_int32]
     L.hxq_gemm.restype = C.c_int

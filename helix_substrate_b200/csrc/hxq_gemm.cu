@@ -214,8 +214,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
 
         // sidecar cursor: lanes 0..ROWS_PER_WARP-1 each follow one of this warp's rows
         const int row_c = o0 + ROWS_PER_WARP * dw + lane;
-        int e_cur = 0, e_end = 0, nc = 0x7fffffff;
-        float nd = 0.f;
+        // (two entries are held ahead: the loads that refill them are not waited for inside the step)
+        int e_cur = 0, e_end = 0, nc = 0x7fffffff, nc1 = 0x7fffffff;
+        float nd = 0.f, nd1 = 0.f;
         if (a.rowptr != nullptr && lane < ROWS_PER_WARP && row_c < a.out_features) {
             e_cur = a.rowptr[row_c];
             e_end = a.rowptr[row_c + 1];
@@ -228,6 +229,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                 e_cur = lo;
             }
             if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
+            if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; }
         }
 
         for (int ks = 0; ks < KS; ++ks) {
@@ -286,7 +288,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                     *reinterpret_cast<__nv_bfloat16*>(st + r * 128 + ((((c >> 3) ^ (r & 7)) << 4) | ((c & 7) << 1))) =
                         __float2bfloat16_rn(wv);
                     ++e_cur;
-                    if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; } else { nc = 0x7fffffff; }
+                    nc = nc1; nd = nd1;
+                    if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; } else { nc1 = 0x7fffffff; }
                 }
             }
             sm100::fence_proxy_async_smem();

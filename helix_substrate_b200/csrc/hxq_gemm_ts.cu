@@ -5,22 +5,22 @@
 // per weight, each weight used for at most 128 tokens), so the kernel is built like the decode kernel,
 // not like a GEMM: everything that is not a lookup is kept off the shared-memory data path.
 //
-//   * CTA tile: 128 output rows x BN tokens (BN = 32, 64, 128), K walked in stages of 128 columns,
+//   * CTA tile: 128 output rows x BN tokens (BN = 16, 32, 64, 128), K walked in stages of 128 columns,
 //     one CTA per SM; small row-tile grids split K over gridDim.z (fp32 partials + a fixed-order sum).
 //   * warp 0, one lane: TMA producer.  Per stage one 128 x 128 box of index bytes and two 64-column
 //     boxes of bf16 activations, all 128-byte swizzled, on one mbarrier.  No multicast, no cluster.
-//   * warps 2..9: dequantisers, ONE THREAD PER OUTPUT ROW and 64-column half of the stage.  A thread
-//     reads its row's 64 codes with four conflict-free 16-byte loads (the swizzle spreads eight rows
-//     over all banks), looks each up in the lane-replicated codebook (one byte-permute + one load per
-//     weight, bank == lane), applies its (row, group) scale and offset in fp32, packs pairs to bf16
-//     and stores its 32 registers straight into the A operand's columns of tensor memory
-//     (tcgen05.st 32x32b: TMEM lane == output row).  Scale/offset, row pointer and sidecar cursor
-//     are thread-local: there is no cross-lane step anywhere.
+//   * warps 2..17: dequantisers, ONE THREAD PER OUTPUT ROW and 32-column quarter of the stage.  A
+//     thread reads its row's 32 codes with two conflict-free 16-byte loads (the swizzle spreads eight
+//     rows over all banks), looks each up in the lane-replicated codebook (one byte-permute + one
+//     load per weight, bank == lane), applies its (row, group) scale and offset in fp32, adds the
+//     row's sidecar deltas that fall into its columns, packs pairs to bf16 and stores its 16
+//     registers straight into the A operand's columns of tensor memory (tcgen05.st 32x32b: TMEM
+//     lane == output row).  Scale/offset and the sidecar cursor are thread-local: there is no
+//     cross-lane step anywhere.
 //   * warp 1, one lane: issues tcgen05.mma kind::f16 with A from tensor memory and B (activations,
 //     K-major, 128-byte swizzle) from shared memory into the fp32 accumulator in tensor memory, and
 //     commits the stage back to the producer.
-//   * epilogue (the dequantising warps): accumulator -> registers, + the row's sidecar entries as
-//     fp32 delta * x (a few entries per row: their activations come through L1/L2), + bias, store.
+//   * epilogue (the dequantising warps): accumulator -> registers, + bias, store.
 //
 // Every mbarrier wait is clock-bounded; a wait that gives up raises a CTA-wide abort flag and the
 // global status word (HXQ_E_TIMEOUT), in-flight copies are given time to land and tensor memory is
@@ -44,7 +44,7 @@ namespace gemmts {
 
 constexpr int BM = 128;             // output rows per CTA = UMMA M = TMEM lanes
 constexpr int KS = 128;             // K columns per stage
-constexpr int DEQ_WARPS = 8;        // warps w and w + 4 share a TMEM lane quarter and split the stage's K halves
+constexpr int DEQ_WARPS = 16;       // four warps per TMEM lane quarter, each takes 32 of a stage's 128 columns
 constexpr int NUM_THREADS = 32 * (2 + DEQ_WARPS);
 constexpr int LUT_BYTES = 256 * 256;            // entry c, lane l at c * 256 + l * 4, base on a 64 KB boundary
 constexpr int IDX_BYTES = BM * KS;              // 16 KB
@@ -87,17 +87,20 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
         : "memory");
 }
 
-// 32 registers per thread -> 32 consecutive columns of this thread's TMEM lane (whole warp).
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+// 16 registers per thread -> 16 consecutive columns of this thread's TMEM lane (whole warp).
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+// One bf16 half of a packed pair += delta (the value is re-rounded to bf16).
+__device__ __forceinline__ uint32_t add_to_half(uint32_t pair, int hi, float delta) {
+    const float v = __uint_as_float(hi ? (pair & 0xffff0000u) : (pair << 16)) + delta;
+    const uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+    return hi ? ((pair & 0x0000ffffu) | (b << 16)) : ((pair & 0xffff0000u) | b);
 }
 __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -105,7 +108,8 @@ __device__ __forceinline__ void tmem_st_wait() {
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x, const Args a) {
+gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x,
+               const __grid_constant__ CUtensorMap map_pf, const Args a) {
     constexpr int B_BYTES = BN * KS * 2;                 // two [BN x 64] bf16 sub-tiles
     constexpr int STAGE_BYTES = IDX_BYTES + B_BYTES;     // multiple of 1024
     extern __shared__ __align__(1024) char smem_raw[];
@@ -149,6 +153,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
         sm100::fence_barrier_init();
         sm100::prefetch_tensormap(&map_idx);
         sm100::prefetch_tensormap(&map_x);
+        sm100::prefetch_tensormap(&map_pf);
     }
     if (warp == 1) {
         sm100::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -161,17 +166,30 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
     __syncthreads();
     sm100::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a0 = tmem_base + (uint32_t)BN;       // A stages follow the accumulator's BN columns
+    const uint32_t tmem_a0 = tmem_base + (uint32_t)(BN < 32 ? 32 : BN);   // A stages follow the accumulator's columns
 
     if (STAGES < 2) {   // cannot happen with the sizes above; never run a pipeline that cannot make progress
         if (threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, HXQ_E_SHAPE);
     } else if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            // A stage's index box is 128 bytes of each of 128 rows: fetched like that from DRAM, every
+            // access would open a page for 128 bytes.  So the same rows are pulled into L2 ahead of time
+            // in boxes four stages (512 bytes per row) wide, and the stage loads then hit L2.
+            auto prefetch_box = [&](int ks4) {     // ks4: first stage of the box, relative to KS0
+                const int col = (KS0 + ks4) * KS;
+                if (ks4 < NK && col < a.in_features)
+                    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                                 :: "l"(reinterpret_cast<uint64_t>(&map_pf)), "r"(col / 4), "r"(o0) : "memory");
+            };
+            prefetch_box(0);
+            prefetch_box(4);
+            prefetch_box(8);
             int armed = 0;
             for (int ks = 0; ks < NK; ++ks) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+                if ((ks & 3) == 0) prefetch_box(ks + 12);
                 if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                 char* st = stage_ptr(s);
                 sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)STAGE_BYTES);
@@ -212,20 +230,19 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
         // ------------------------------------------------------------ dequantising warps
         const int dw = warp - 2;
         const int quarter = warp & 3;                 // TMEM lanes this warp may touch: [32 * quarter, +32)
-        const int khalf = (dw >> 2) & 1;              // which 64 columns of each stage
-        // warps 2..9: warp & 3 takes the values 2,3,0,1,2,3,0,1: every quarter gets exactly two warps, dw>>2 = 0 and 1
+        const int kq = dw >> 2;                       // which 32 columns of each stage (warps 2..17: every quarter gets kq = 0..3 once)
         const int r = 32 * quarter + lane;            // row inside the CTA tile == TMEM lane
         const int row = o0 + r;
         const bool row_ok = row < a.out_features;
         const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
         const bool affine = a.group_size > 0;
         const int g_base = affine ? a.col0 / a.group_size : 0;
-        const uint32_t t_row = tmem_a0 + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(khalf * 32);
+        const uint32_t t_row = tmem_a0 + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(kq * 16);
 
         auto load_st = [&](int ks, float& s, float& t) {
             s = 1.f; t = 0.f;
             if (affine && row_ok) {
-                int g = (a.col0 + (KS0 + ks) * KS + khalf * 64) / a.group_size - g_base;
+                int g = (a.col0 + (KS0 + ks) * KS + kq * 32) / a.group_size - g_base;
                 g = g < a.n_groups ? g : a.n_groups - 1;      // K tail: those activations are zero
                 const int64_t o = (int64_t)row * a.ld_st + g;
                 if (a.st_dtype == HXQ_F32) {
@@ -237,8 +254,22 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
                 }
             }
         };
+        // sidecar cursor of this row: entries are sorted by column; this thread takes those inside its
+        // 32 columns of every stage and steps over the others
+        // (two entries are held ahead: the loads that refill them are not waited for inside the stage)
+        int e_cur = 0, e_end = 0, nc = 0x7fffffff, nc1 = 0x7fffffff;
+        float nd = 0.f, nd1 = 0.f;
+        if (a.rowptr != nullptr && row_ok) {
+            e_cur = a.rowptr[row];
+            e_end = a.rowptr[row + 1];
+            const int k_first = KS0 * KS;
+            while (e_cur < e_end && a.cols[e_cur] < k_first) ++e_cur;
+            if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
+            if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; }
+        }
         float sc_n, of_n;
         load_st(0, sc_n, of_n);
+        int done = 0;
         for (int ks = 0; ks < NK; ++ks) {
             const int s = ks % STAGES;
             const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
@@ -246,10 +277,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
             if (ks + 1 < NK) load_st(ks + 1, sc_n, of_n);
             if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
             const uint32_t idx_row = sm100::smem_u32(stage_ptr(s)) + (uint32_t)(r * 128);
-            uint32_t out[32];
+            uint32_t out[16];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {     // 16 codes per load: chunk 4 * khalf + c of the row, swizzled by the row
-                const uint32_t addr = idx_row + ((uint32_t)((4 * khalf + c) ^ (r & 7)) << 4);
+            for (int c = 0; c < 2; ++c) {     // 16 codes per load: chunk 2 * kq + c of the row, swizzled by the row
+                const uint32_t addr = idx_row + ((uint32_t)((2 * kq + c) ^ (r & 7)) << 4);
                 uint32_t w[4];
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
 #pragma unroll
@@ -262,61 +293,84 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
                     out[c * 8 + (j >> 1)] = pack_bf16x2(fmaf(v0, sc, of), fmaf(v1, sc, of));
                 }
             }
-            tmem_st_32x32(t_row + (uint32_t)(s * A_COLS), out);
+            // sidecar entries of this row inside this stage: mine are patched into the packed registers
+            // (a jump per entry instead of a dynamically indexed register array), the others skipped
+            {
+                const int k_lo = (KS0 + ks) * KS + kq * 32;
+                const int k_st = (KS0 + ks + 1) * KS;
+                while (nc < k_st) {
+                    const int j = nc - k_lo;
+                    if (j >= 0 && j < 32) {
+                        const int hi = j & 1;
+                        switch (j >> 1) {
+                            case 0: out[0] = add_to_half(out[0], hi, nd); break;
+                            case 1: out[1] = add_to_half(out[1], hi, nd); break;
+                            case 2: out[2] = add_to_half(out[2], hi, nd); break;
+                            case 3: out[3] = add_to_half(out[3], hi, nd); break;
+                            case 4: out[4] = add_to_half(out[4], hi, nd); break;
+                            case 5: out[5] = add_to_half(out[5], hi, nd); break;
+                            case 6: out[6] = add_to_half(out[6], hi, nd); break;
+                            case 7: out[7] = add_to_half(out[7], hi, nd); break;
+                            case 8: out[8] = add_to_half(out[8], hi, nd); break;
+                            case 9: out[9] = add_to_half(out[9], hi, nd); break;
+                            case 10: out[10] = add_to_half(out[10], hi, nd); break;
+                            case 11: out[11] = add_to_half(out[11], hi, nd); break;
+                            case 12: out[12] = add_to_half(out[12], hi, nd); break;
+                            case 13: out[13] = add_to_half(out[13], hi, nd); break;
+                            case 14: out[14] = add_to_half(out[14], hi, nd); break;
+                            default: out[15] = add_to_half(out[15], hi, nd); break;
+                        }
+                    }
+                    ++e_cur;
+                    nc = nc1; nd = nd1;
+                    if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; } else { nc1 = 0x7fffffff; }
+                }
+            }
+            __syncwarp();
+            // the previous stage's store has had this stage's lookups to complete: hand that stage over
+            // now, then start this stage's store
+            if (ks > 0) {
+                tmem_st_wait();
+                sm100::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) sm100::mbar_arrive(&a_full[(ks - 1) % STAGES]);
+            }
+            tmem_st_32x16(t_row + (uint32_t)(s * A_COLS), out);
+            done = ks + 1;
+        }
+        if (done > 0) {   // the last stage stored (a wait that gave up leaves `done` at the last stored stage)
             tmem_st_wait();
             sm100::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) sm100::mbar_arrive(&a_full[s]);
+            if (lane == 0) sm100::mbar_arrive(&a_full[(done - 1) % STAGES]);
         }
 
         // ------------------------------------------------------------ epilogue
-        // warps of one quarter split the token columns: dw >> 2 == 0 takes the first half
+        // the four warps of a quarter split the token columns
         {
-            constexpr int COLS_PER_WARP = BN / 2;        // 16, 32 or 64
-            const int c_lo = khalf * COLS_PER_WARP;
-            if (sm100::mbar_wait(acc_full, 0u, abort_flag)) {
+            constexpr int COLS_PER_WARP = BN / 4 < 8 ? 8 : BN / 4;   // 8, 16 or 32 (16 tokens: two of the four warps)
+            const int c_lo = kq * COLS_PER_WARP;
+            if (c_lo < BN && sm100::mbar_wait(acc_full, 0u, abort_flag)) {
                 sm100::tc_fence_after_sync();
                 float* part = a.partial ? a.partial + (int64_t)blockIdx.z * a.M * a.out_features : nullptr;
                 const float bias = (a.bias != nullptr && row_ok && part == nullptr) ? a.bias[row] : 0.f;
-                // this row's sidecar entries inside this CTA's K range
-                int e0 = 0, e1 = 0;
-                if (a.rowptr != nullptr && row_ok) {
-                    e0 = a.rowptr[row];
-                    e1 = a.rowptr[row + 1];
-                    const int k_lo = KS0 * KS, k_hi = (KS0 + NK) * KS;
-                    while (e0 < e1 && a.cols[e0] < k_lo) ++e0;
-                    while (e1 > e0 && a.cols[e1 - 1] >= k_hi) --e1;
-                }
 #pragma unroll 1
-                for (int c0 = c_lo; c0 < c_lo + COLS_PER_WARP; c0 += 16) {
+                for (int c0 = c_lo; c0 < c_lo + COLS_PER_WARP; c0 += 8) {
                     if (m0 + c0 >= a.M) break;           // warp-uniform
-                    uint32_t v[16];
+                    uint32_t v[8];
                     asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                         : "r"(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0)
                         : "memory");
                     sm100::tmem_ld_wait();
-                    float acc[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
-                    for (int e = e0; e < e1; ++e) {
-                        const int c = a.cols[e];
-                        const float dl = a.deltas[e];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int m = m0 + c0 + j;
-                            if (m < a.M) acc[j] = fmaf(dl, __bfloat162float(a.xb[(int64_t)m * a.ldxb + c]), acc[j]);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < 8; ++j) {
                         const int m = m0 + c0 + j;
                         if (row_ok && m < a.M) {
-                            if (part != nullptr) part[(int64_t)m * a.out_features + row] = acc[j];
-                            else store_from_f32(a.y, (int64_t)m * a.ldy + row, acc[j] + bias, a.y_dtype);
+                            const float acc = __uint_as_float(v[j]);
+                            if (part != nullptr) part[(int64_t)m * a.out_features + row] = acc;
+                            else store_from_f32(a.y, (int64_t)m * a.ldy + row, acc + bias, a.y_dtype);
                         }
                     }
                 }
@@ -343,7 +397,7 @@ static int sm_count() {
     return n_sm;
 }
 
-static int pick_bn(int M) { return M > 64 ? 128 : (M > 32 ? 64 : 32); }
+static int pick_bn(int M) { return M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)); }
 
 // K slices per output tile: enough CTAs to fill the GPU when the row-tile grid alone does not, at
 // least four stages each.
@@ -379,8 +433,8 @@ size_t split_bytes(const hxq_desc* d, int32_t M) {
 }
 
 template <int BN>
-static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, int grid_m, int grid_o, int splits,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const CUtensorMap& mp, const Args& a, int grid_m, int grid_o,
+                  int splits, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -389,7 +443,7 @@ static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, i
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mi, mx, a);
+    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mi, mx, mp, a);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
@@ -404,6 +458,11 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
         return HXQ_E_DEVICE;
     if (!gemm::make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, (uint64_t)d->in_features, (uint64_t)M,
                            (uint64_t)ldxb * 2, 64, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return HXQ_E_DEVICE;
+    // the same index matrix as 32-bit words, in boxes of 512 bytes x 128 rows: L2 prefetches only
+    CUtensorMap mp;
+    if (!gemm::make_map_2d(&mp, CU_TENSOR_MAP_DATA_TYPE_UINT32, d->indices, (uint64_t)d->in_features / 4,
+                           (uint64_t)d->out_features, (uint64_t)d->ld_idx, 128, BM, CU_TENSOR_MAP_SWIZZLE_NONE))
         return HXQ_E_DEVICE;
     Args a;
     a.cb = d->codebook; a.scales = d->scales; a.offsets = d->offsets;
@@ -429,9 +488,10 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
         splits = 1;
     }
     int st;
-    if (BN == 128) st = launch<128>(mi, mx, a, grid_m, grid_o, splits, stream);
-    else if (BN == 64) st = launch<64>(mi, mx, a, grid_m, grid_o, splits, stream);
-    else st = launch<32>(mi, mx, a, grid_m, grid_o, splits, stream);
+    if (BN == 128) st = launch<128>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
+    else if (BN == 64) st = launch<64>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
+    else if (BN == 32) st = launch<32>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
+    else st = launch<16>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
     if (st != HXQ_OK || splits == 1) return st;
     gemm::launch_splitk_reduce(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy, stream);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;

@@ -75,6 +75,7 @@ struct GemvArgs {
     int32_t max_parts;  // CTAs that can share one row block
     int32_t rbl_max;    // row blocks a CTA can touch (slots in shared memory)
     int32_t slot_bytes; // lean kernel: bytes of reduction slots after the table (multiple of 128)
+    int32_t tail_lanes; // lean kernel: lanes of the last chunk that hold columns (32 when it is whole)
 };
 
 struct GemvPlan {
@@ -499,7 +500,7 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 
 // ---- lean kernel: shapes where every unit is whole ---------------------------------------
 //
-// OUT % 8 == 0, IN % 512 == 0, no column offset inside a group, group size 0 or 128, 16-byte
+// OUT % 8 == 0, IN % 128 == 0, no column offset inside a group, group size 0 or 128, 16-byte
 // aligned activations: no unit touches an edge, so the per-unit code carries no bounds logic
 // at all.  Same unit, table and butterfly as gemv_kernel; what differs is the bookkeeping:
 //  * index bytes travel global -> shared with 16-byte asynchronous copies (each lane copies, and
@@ -573,7 +574,7 @@ __device__ __forceinline__ void x_lane16(const void* xrow, int col, uint64_t (&x
     }
 }
 
-template <int MP, int XDT, int STM, bool SIDE>
+template <int MP, int XDT, int STM, bool SIDE, bool TAIL>
 __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1)
 gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     extern __shared__ __align__(1024) char dyn_smem[];
@@ -630,6 +631,9 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     const char* const xbase = reinterpret_cast<const char*>(a.x);
     const uint32_t ld = (uint32_t)a.ld_idx;
     const int d_rb = W / nch, d_ch = W - d_rb * nch;
+    // a last chunk with fewer than 512 columns (whole 128-column groups): lanes past its end fetch from lane 0's
+    // addresses and hold zero activations, so they add nothing
+    const bool tail_lane = TAIL && lane >= a.tail_lanes;
     // sidecar carriers of row block rb: the units with (chunk - rb) mod nch < n_car
     const int n_car = nch < kLeanCarriers ? nch : kLeanCarriers;
     const int own_step = d_rb % nch;
@@ -665,12 +669,14 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
             }
         }
 #else
+        const bool cut = tail_lane && ch == nch - 1;
+        const uint8_t* pq = cut ? p - lane * 16 : p;
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                         :: "r"((buf ? ring_q1 : ring_q0) + r * kChunk), "l"(p + (uint64_t)ld * (uint32_t)r) : "memory");
+                         :: "r"((buf ? ring_q1 : ring_q0) + r * kChunk), "l"(pq + (uint64_t)ld * (uint32_t)r) : "memory");
         if (with_x) {   // warp-uniform: the unit's chunk differs from the one whose activations are in registers
-            const char* xg = xbase + (size_t)(ch * kChunk + lane * 16) * (xs_lane >> 4);
+            const char* xg = xbase + (size_t)(ch * kChunk + (cut ? 0 : lane * 16)) * (xs_lane >> 4);
 #pragma unroll
             for (int m = 0; m < MP; ++m) {
                 if (m < M) {
@@ -687,12 +693,16 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
 #endif
         f.s = 1.f; f.t = 0.f;
         if (affine) {
+#if HXQ_GEMV_TMA
+            const bool cut = tail_lane && ch == nch - 1;
+#endif
+            const int sq = cut ? so - h_l : so;
             if (st_f32) {
-                f.s = reinterpret_cast<const float*>(a.scales)[so];
-                f.t = reinterpret_cast<const float*>(a.offsets)[so];
+                f.s = reinterpret_cast<const float*>(a.scales)[sq];
+                f.t = reinterpret_cast<const float*>(a.offsets)[sq];
             } else {
-                f.s = __half2float(reinterpret_cast<const __half*>(a.scales)[so]);
-                f.t = __half2float(reinterpret_cast<const __half*>(a.offsets)[so]);
+                f.s = __half2float(reinterpret_cast<const __half*>(a.scales)[sq]);
+                f.t = __half2float(reinterpret_cast<const __half*>(a.offsets)[sq]);
             }
         }
         f.e = 0; f.e1 = 0; f.last = false;
@@ -716,8 +726,13 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
     float xsum[MP];
     int cur_ch = -1;
     auto set_x = [&](float (&xr)[MP][16], int c) {
+        const bool cut = tail_lane && c == nch - 1;
 #pragma unroll
         for (int m = 0; m < MP; ++m) {
+            if (cut) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) xr[m][j] = 0.f;
+            }
             float sx = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -738,7 +753,8 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
 #pragma unroll
         for (int m = 0; m < MP; ++m) {
             uint64_t t8[8];
-            if (m < M) x_lane16<XDT>(xbase + (size_t)m * ldx * (XDT == HXQ_F32 ? 4 : 2), c * kChunk + lane * 16, t8);
+            if (m < M) x_lane16<XDT>(xbase + (size_t)m * ldx * (XDT == HXQ_F32 ? 4 : 2),
+                                     c * kChunk + ((tail_lane && c == nch - 1) ? 0 : lane * 16), t8);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 float lo = 0.f, hi = 0.f;
@@ -1164,7 +1180,11 @@ static bool gemv_lean_shape(const hxq_desc* d, const GemvPlan& p, bool x_vec) {
     return false;
 #endif
     if (p.grid <= 0 || p.kbase != 0 || !x_vec) return false;
-    if (d->in_features % kChunk != 0 || d->out_features % kRows != 0) return false;
+    // whole 8-row blocks; whole 128-column groups (a short last chunk is masked by lane)
+    if (d->in_features % 128 != 0 || d->out_features % kRows != 0) return false;
+#if HXQ_GEMV_TMA
+    if (d->in_features % kChunk != 0) return false;   // the bulk-copy variant reads whole chunks of activations
+#endif
     if (d->group_size != 0 && d->group_size != 128) return false;
     return (int64_t)d->out_features * (d->group_size ? d->ld_st : 0) <= 0x7fffffffLL;
 }
@@ -1197,14 +1217,14 @@ static int launch_edge(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream
     return cudaLaunchKernelEx(&cfg, gemv_kernel<MP>, a) == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
-// The lean kernel is compiled once per (tokens per launch, activation type, scale/offset type, sidecar):
+// The lean kernel is compiled once per (tokens per launch, activation type, scale/offset type, sidecar, short last chunk):
 // none of those is looked at inside the unit loop.
-template <int MP, int XDT, int STM, bool SIDE>
-static int launch_lean_one(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
+template <int MP, int XDT, int STM, bool SIDE, bool TAIL>
+static int launch_lean_tail(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = gemv_lean_kernel<MP, XDT, STM, SIDE>;
+    auto kern = gemv_lean_kernel<MP, XDT, STM, SIDE, TAIL>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kLeanSmemBytes) != cudaSuccess)
             return HXQ_E_DEVICE;
@@ -1213,6 +1233,11 @@ static int launch_lean_one(const GemvArgs& a, const GemvPlan& p, const CUtensorM
     cudaLaunchAttribute attr[1];
     const cudaLaunchConfig_t cfg = gemv_launch_config(p, kLeanSmemBytes, stream, attr);
     return cudaLaunchKernelEx(&cfg, kern, tmap, a) == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+template <int MP, int XDT, int STM, bool SIDE>
+static int launch_lean_one(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
+    return a.tail_lanes < 32 ? launch_lean_tail<MP, XDT, STM, SIDE, true>(a, p, tmap, stream)
+                             : launch_lean_tail<MP, XDT, STM, SIDE, false>(a, p, tmap, stream);
 }
 template <int MP, int XDT>
 static int launch_lean_st(const GemvArgs& a, const GemvPlan& p, const CUtensorMap& tmap, cudaStream_t stream) {
@@ -1246,7 +1271,7 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
     a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     a.scratch = nullptr; a.counters = nullptr;
-    a.units = 0; a.kbase = 0; a.nch = 1; a.nrb = 0; a.max_parts = 1; a.rbl_max = 1; a.x_vec = 0; a.slot_bytes = 0;
+    a.units = 0; a.kbase = 0; a.nch = 1; a.nrb = 0; a.max_parts = 1; a.rbl_max = 1; a.x_vec = 0; a.slot_bytes = 0; a.tail_lanes = 32;
     const int xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
 
     const int n_sm = sm_count();
@@ -1284,6 +1309,7 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
         CUtensorMap tmap;
         if (lean) lean = gemv_index_map(&tmap, d);
         a.slot_bytes = lean ? lean_slot_bytes(p, MP) : 0;
+        a.tail_lanes = (lean && d->in_features % kChunk) ? (d->in_features % kChunk) / 16 : 32;
         int st;
         if (MP == 1) st = launch_fast<1>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
         else if (MP == 2) st = launch_fast<2>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);

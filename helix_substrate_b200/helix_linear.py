@@ -3,7 +3,7 @@
 Same constructor, buffer names, state-dict keys and helper functions as the
 reference module (helix_substrate/helix_linear.py:53-1499), so model code and
 checkpoints written for it keep working.  What differs is underneath: every
-forward mode runs the one CUDA path (hxq_gemv for <= 16 tokens, hxq_gemm above),
+forward mode runs the one CUDA path (hxq_gemv for a few tokens, hxq_gemm above),
 a CPU input raises instead of falling back, and an optional per-group affine
 (``group_scales`` / ``group_offsets`` / ``group_size``) is part of the weight:
 
@@ -21,7 +21,7 @@ import numpy as np
 import torch
 import torch.nn as nn
 
-from .packed import HxqWeight, csr_from_positions
+from .packed import HxqWeight, csr_from_positions, uses_gemv
 
 
 @dataclass(frozen=True)
@@ -303,7 +303,7 @@ class HelixLinear(nn.Module):
         svd = self.has_svd and not self._cell_skip_svd
         y = w.matmul(x2, out_dtype=torch.float32 if svd else out_dtype)
         self._last_dispatch = {
-            "dispatch_selected": "hxq_gemv_sm100a" if x2.shape[0] <= 16 else "hxq_gemm_sm100a",
+            "dispatch_selected": "hxq_gemv_sm100a" if uses_gemv(x2.shape[0], x2.dtype) else "hxq_gemm_sm100a",
             "tokens": int(x2.shape[0]), "vq_dim": 1,
         }
         if svd:  # rank-r residual as two small dense products (triton_vq_matmul.py:715-721)

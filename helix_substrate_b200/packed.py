@@ -14,7 +14,15 @@ from ._lib import HxqDesc, HXQ_F32, HXQ_F16, HXQ_BF16
 
 _DT = {torch.float32: HXQ_F32, torch.float16: HXQ_F16, torch.bfloat16: HXQ_BF16}
 
-GEMV_MAX_M = 16  # above this the tensor-core kernel takes over
+GEMV_MAX_M = 16      # most tokens hxq_gemv takes per call
+GEMV_MAX_M_16BIT = 4  # bf16 / fp16 activations: beyond four tokens the tensor-memory kernel is faster
+
+
+def uses_gemv(M: int, x_dtype: torch.dtype) -> bool:
+    """Which product a call of M tokens runs by default: the fp32-accumulate streaming kernel
+    (hxq_gemv: one launch per four tokens, every launch re-reading the weights) up to 16 tokens
+    of fp32 activations or 4 tokens of 16-bit ones, the tensor-core kernels (bf16 operands) above."""
+    return M <= (GEMV_MAX_M if x_dtype == torch.float32 else GEMV_MAX_M_16BIT)
 
 
 def _dt(t: torch.dtype) -> int:
@@ -131,7 +139,7 @@ class HxqWeight:
             return out
         L = _lib.lib()
         stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        use_gemv = (M <= GEMV_MAX_M) if force is None else (force == "gemv")
+        use_gemv = uses_gemv(M, x.dtype) if force is None else (force == "gemv")
         with torch.cuda.device(self.device):
             if use_gemv:
                 y, m0 = out, 0

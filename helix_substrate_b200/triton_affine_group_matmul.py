@@ -68,12 +68,38 @@ def pack6(indices: torch.Tensor) -> torch.Tensor:
 def fused_affine_group_matmul_packed6(x: torch.Tensor, packed_indices: torch.Tensor, scales: torch.Tensor,
                                       offsets: torch.Tensor, out_features: int, in_features: int,
                                       group_size: int = 128, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """The reference's 6-bit variant (helix_substrate/triton_affine_group_matmul.py:256-298), any N:
-    the packed bytes are expanded to one byte per index on the device (torch ops, every call: a
-    caller that decodes repeatedly should keep ``unpack6``'s result and use fused_affine_group_matmul)
-    and the product runs on the ordinary kernels."""
+    """The reference's 6-bit variant (helix_substrate/triton_affine_group_matmul.py:256-298), any N.
+    Up to 16 tokens the packed bytes are unpacked INSIDE the kernel (``hxq_gemv_packed6``: the
+    weight stream is 0.75 byte per weight).  More tokens, or shapes that kernel does not take
+    (IN or group size not a multiple of 16), expand to one byte per index first (torch ops) and
+    run on the ordinary kernels - keep ``unpack6``'s result if you do that repeatedly."""
+    import ctypes as C
+    from . import _lib
     assert x.is_cuda and packed_indices.is_cuda
     assert x.ndim == 2 and x.shape[1] == in_features
+    assert packed_indices.dtype == torch.uint8
+    assert packed_indices.numel() == out_features * in_features * 3 // 4, "packed size does not match OUT x IN x 3/4"
+    M = x.shape[0]
+    dt = {torch.float32: _lib.HXQ_F32, torch.float16: _lib.HXQ_F16, torch.bfloat16: _lib.HXQ_BF16}
+    if 0 < M <= 16 and in_features % 16 == 0 and group_size % 16 == 0 and x.dtype in dt:
+        assert in_features % group_size == 0, f"IN ({in_features}) must be a multiple of group_size ({group_size})"
+        if scales.dtype not in (torch.float16, torch.float32):
+            scales, offsets = scales.float(), offsets.float()
+        scales, offsets = scales.contiguous(), offsets.to(scales.dtype).contiguous()
+        assert scales.shape == (out_features, in_features // group_size) and offsets.shape == scales.shape
+        packed = packed_indices.contiguous()
+        xc = x if x.stride(1) == 1 else x.contiguous()
+        b = None if bias is None else bias.float().contiguous()
+        y = torch.empty(M, out_features, device=x.device, dtype=torch.float32)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().hxq_gemv_packed6(
+                C.c_void_p(packed.data_ptr()), out_features, in_features, C.c_void_p(scales.data_ptr()),
+                C.c_void_p(offsets.data_ptr()), _lib.HXQ_F32 if scales.dtype == torch.float32 else _lib.HXQ_F16,
+                scales.stride(0), group_size, None if b is None else C.c_void_p(b.data_ptr()),
+                C.c_void_p(xc.data_ptr()), dt[x.dtype], M, xc.stride(0), C.c_void_p(y.data_ptr()), _lib.HXQ_F32,
+                y.stride(0), C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+        _lib.check(st, "hxq_gemv_packed6")
+        return y
     idx = unpack6(packed_indices, out_features, in_features)
     return fused_affine_group_matmul(x, idx, scales, offsets, group_size=group_size, bias=bias)
 

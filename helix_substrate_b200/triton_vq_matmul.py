@@ -1,7 +1,7 @@
 """fused_vq_matmul: the operator behind HelixLinear, same name and signature as
 the reference's Triton operator (helix_substrate/triton_vq_matmul.py:521-727)
 so existing imports keep working - but the body is the sm_100a C-ABI library
-(hxq_gemv for N <= 16, hxq_gemm above).  No Triton is involved."""
+(hxq_gemv for a few tokens, hxq_gemm above: packed.uses_gemv).  No Triton is involved."""
 
 from __future__ import annotations
 
@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .packed import HxqWeight
+from .packed import HxqWeight, uses_gemv
 
 KERNEL_VERSION = "hxq_b200_v1"
 KERNEL_IMPL = "libhxq_b200"
@@ -122,8 +122,9 @@ def fused_vq_matmul(
     except _lib.HxqError as e:
         raise RuntimeError(f"hxq kernel launch failed: {e}. N={N}, IN={IN}, OUT={OUT}. No silent fallback.") from e
     if _dispatch_log is not None:
-        _dispatch_log["dispatch_selected"] = "hxq_gemv_sm100a" if N <= 16 else "hxq_gemm_sm100a"
-        _dispatch_log["block_config"] = "unit8x512" if N <= 16 else "umma128"
+        gemv = uses_gemv(N, x.dtype)
+        _dispatch_log["dispatch_selected"] = "hxq_gemv_sm100a" if gemv else "hxq_gemm_sm100a"
+        _dispatch_log["block_config"] = "unit8x512" if gemv else "umma128"
         _dispatch_log["vq_dim"] = vq_dim
     if svd_U is not None:
         xf = x.float()

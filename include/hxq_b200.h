@@ -137,9 +137,25 @@ int hxq_gemv_static(const hxq_desc* d, const void* x, int x_dtype, int32_t M, in
                     void* y, int y_dtype, int64_t ldy, hxq_stream_t stream);
 
 /*
+ * Decode-time product over 6-bit packed indices, M <= 16: four codes in three bytes
+ * (b0 | b1 << 8 | b2 << 16 holds v0..v3 from the low bits up), unpacked inside the kernel, the
+ * code itself being the value:  y[m, o] = sum_i x[m, i] * (code[o, i] * s[o, i / G] + t[o, i / G])
+ * + bias.  Replaces fused_affine_group_matmul_packed6 / _affine_group_packed6_kernel
+ * (helix_substrate/triton_affine_group_matmul.py:180-298; the reference serves one token only).
+ * packed: [out_features, in_features * 3 / 4] bytes, 4-byte aligned; in_features and group_size
+ * multiples of 16; scales / offsets [out_features, ld_st] of st_dtype (HXQ_F32 or HXQ_F16).
+ */
+int hxq_gemv_packed6(const uint8_t* packed, int32_t out_features, int32_t in_features,
+                     const void* scales, const void* offsets, int st_dtype, int32_t ld_st,
+                     int32_t group_size, const float* bias, const void* x, int x_dtype, int32_t M,
+                     int64_t ldx, void* y, int y_dtype, int64_t ldy, hxq_stream_t stream);
+
+/*
  * Prefill-time product for any M (meant for M >= 17):  same contract as
- * hxq_gemv but weights are dequantised to bf16 tiles in shared memory and
- * contracted on the tcgen05 tensor cores with fp32 TMEM accumulators.
+ * hxq_gemv but weights are dequantised to bf16 and contracted on the tcgen05
+ * tensor cores with fp32 TMEM accumulators: up to 128 tokens the dequantised
+ * tile goes to the MMA through tensor memory (one thread per output row), above
+ * that through 128-byte swizzled shared-memory tiles.
  * Replaces fused_vq_matmul at N > 16 (_vq_gather_matmul_tiled_kernel,
  * helix_substrate/triton_vq_matmul.py:249-334,634-661, + scatter_add sidecar
  * :693-698) and _affine_group_tiled_kernel

@@ -43,6 +43,13 @@ def test_argument_validation_without_a_device():
     assert L.hxq_gemv(C.byref(d), None, 0, 1, 0, None, 0, 0, None, 0, None) == _lib.HXQ_E_ARG
     assert L.hxq_dequant(None, 0, 1, None, 0, 0, None) == _lib.HXQ_E_ARG
     assert L.hxq_gemv_workspace_bytes(C.byref(d), 1) == 0
+    # 6-bit packed product: nulls, token count, shapes that are not whole 16-code pieces
+    assert L.hxq_gemv_packed6(None, 8, 64, None, None, 0, 1, 64, None, None, 0, 1, 64, None, 0, 8, None) == _lib.HXQ_E_ARG
+    buf = np.zeros(64, dtype=np.uint8)
+    p = buf.ctypes.data
+    assert L.hxq_gemv_packed6(p, 8, 64, p, p, 0, 1, 64, None, p, 0, 17, 64, p, 0, 8, None) == _lib.HXQ_E_ARG
+    assert L.hxq_gemv_packed6(p, 8, 60, p, p, 0, 1, 60, None, p, 0, 1, 60, p, 0, 8, None) == _lib.HXQ_E_SHAPE
+    assert L.hxq_gemv_packed6(p, 8, 64, p, p, 2, 1, 64, None, p, 0, 1, 64, p, 0, 8, None) == _lib.HXQ_E_DTYPE
 
 
 def test_csr_helper():

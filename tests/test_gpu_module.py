@@ -214,21 +214,32 @@ def test_per_tensor_affine_operator(n_out, n_in, M):
     assert rel_l2(affine_matmul_reference(x, idx, step, offset, bias).double().cpu().numpy(), ref.cpu().numpy()) < 1e-4
 
 
-@pytest.mark.parametrize("M", [1, 3])
-def test_six_bit_packed_affine_group_operator(M):
-    """fused_affine_group_matmul_packed6 (reference: N = 1 only) against the unpacked product."""
+@pytest.mark.parametrize("M", [1, 3, 16, 20])
+@pytest.mark.parametrize("shape", [(72, 512, 128), (40, 3584, 128), (9, 208, 16)])
+def test_six_bit_packed_affine_group_operator(M, shape):
+    """fused_affine_group_matmul_packed6 (reference: N = 1 only): up to 16 tokens the 3-byte groups
+    are unpacked inside the kernel, beyond that the unpacked product runs; both against fp64."""
     from helix_substrate_b200.triton_affine_group_matmul import (
         fused_affine_group_matmul, fused_affine_group_matmul_packed6, pack6)
-    n_out, n_in, G = 72, 512, 128
+    n_out, n_in, G = shape
     gen = torch.Generator(device=DEV).manual_seed(M)
     idx = torch.randint(0, 64, (n_out, n_in), dtype=torch.uint8, device=DEV, generator=gen)
     s = (0.01 + 0.001 * torch.rand(n_out, n_in // G, device=DEV, generator=gen)).half()
     t = (0.02 * torch.randn(n_out, n_in // G, device=DEV, generator=gen)).half()
-    x = torch.randn(M, n_in, device=DEV, generator=gen)
-    y = fused_affine_group_matmul_packed6(x, pack6(idx), s, t, n_out, n_in, G)
-    assert torch.equal(y, fused_affine_group_matmul(x, idx, s, t, G))
+    b = torch.randn(n_out, device=DEV, generator=gen)
     w = idx.double() * s.double().repeat_interleave(G, 1) + t.double().repeat_interleave(G, 1)
-    assert rel_l2(y.double().cpu().numpy(), (x.double() @ w.t()).cpu().numpy()) < 1e-3
+    for xdt in (torch.float32, torch.bfloat16):
+        x = torch.randn(M, n_in, device=DEV, generator=gen).to(xdt)
+        y = fused_affine_group_matmul_packed6(x, pack6(idx), s, t, n_out, n_in, G, bias=b)
+        assert y.dtype == torch.float32 and y.shape == (M, n_out)
+        ref = x.double() @ w.t() + b.double()
+        tol = 1e-3 if M <= 16 else 1e-2
+        assert rel_l2(y.double().cpu().numpy(), ref.cpu().numpy()) < tol
+        y8 = fused_affine_group_matmul(x, idx, s, t, G, bias=b)          # one byte per index, codebook kernels
+        # that product runs fp32-accumulate for fp32 activations up to 16 tokens, bf16 tensor-core operands otherwise
+        exact = M <= (16 if xdt == torch.float32 else 4)
+        assert rel_l2(y.double().cpu().numpy(), y8.double().cpu().numpy()) < (1e-5 if exact else 1e-2)
+        assert torch.equal(y, fused_affine_group_matmul_packed6(x, pack6(idx), s, t, n_out, n_in, G, bias=b))
 
 
 def test_per_tensor_affine_operator_vs_reference_golden():
@@ -238,3 +249,51 @@ def test_per_tensor_affine_operator_vs_reference_golden():
     y = fused_affine_matmul(t(g["x"]), t(g["indices"]), float(g["step"]), float(g["offset"]), t(g["bias"]))
     assert rel_l2(y.cpu().numpy(), g["y"]) < 1e-3
 
+
+
+def test_hf_from_pretrained_model_runs_on_the_kernels(tmp_path):
+    """The load path a user of the reference takes: compress a (tiny) Qwen2, write ONE
+    safetensors checkpoint with its quantization_config, ``import helix_substrate``,
+    ``AutoModelForCausalLM.from_pretrained(dir).cuda()`` - and run it.  The loaded model's
+    logits must equal those of the model the checkpoint was written from (same kernels, same
+    buffers) and agree to bf16 precision with a dense model rebuilt from ``decode_weight()``."""
+    transformers = pytest.importorskip("transformers")
+    import torch.nn as nn
+    import helix_substrate  # noqa: F401  registers the quantizer under the reference's names
+    from helix_substrate_b200 import HelixLinear, hxq_writer_gpu as W, swap_to_helix
+    from helix_substrate_b200.convert_safetensors import save_hxq_checkpoint
+    cfg = transformers.Qwen2Config(vocab_size=256, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                                   rope_theta=1e6, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = transformers.Qwen2ForCausalLM(cfg).eval()
+    dense = transformers.Qwen2ForCausalLM(cfg).eval()
+    dense.load_state_dict(model.state_dict())
+    facs = {}
+    for name, m in model.named_modules():
+        if isinstance(m, nn.Linear) and name != "lm_head":
+            enc = W.compress_weight(m.weight.data.to(DEV), percentile=99.5, group_size=128)
+            facs[name] = HelixLinear(m.in_features, m.out_features, tensor_name=name + ".weight",
+                                     bias=None if m.bias is None else m.bias.data.clone().to(DEV), **enc)
+    swap_to_helix(model, facs)
+    out = save_hxq_checkpoint(model, tmp_path / "ckpt")
+    model = model.to(DEV)
+    loaded = transformers.AutoModelForCausalLM.from_pretrained(out).to(DEV).eval()
+    n_helix = sum(isinstance(m, HelixLinear) for m in loaded.modules())
+    assert n_helix == 14 and isinstance(loaded.lm_head, nn.Linear)
+    # the dense twin carries exactly the dequantised weights
+    with torch.no_grad():
+        for name, m in dense.named_modules():
+            if name in facs:
+                m.weight.copy_(facs[name].decode_weight().cpu())
+    dense = dense.to(DEV)
+    for T in (1, 9, 40):    # decode-sized, GEMV-sized and tensor-core-sized token counts
+        ids = torch.randint(0, 256, (1, T), device=DEV, generator=torch.Generator(device=DEV).manual_seed(T))
+        with torch.no_grad():
+            y_loaded = loaded(ids).logits
+            y_src = model(ids).logits
+            y_dense = dense(ids).logits
+        assert torch.equal(y_loaded, y_src), "the reloaded model must be the model that was saved"
+        tol = 1e-3 if T <= 16 else 1e-2     # fp32-accumulate kernels / bf16 tensor-core operands
+        assert rel_l2(y_loaded.float().cpu().numpy(), y_dense.float().cpu().numpy()) < tol, T
+    assert all(m._last_dispatch is not None for m in loaded.modules() if isinstance(m, HelixLinear))
