@@ -63,6 +63,8 @@ def lib() -> C.CDLL:
     L.hxq_version.restype = C.c_int
     L.hxq_strerror.restype = C.c_char_p
     L.hxq_strerror.argtypes = [C.c_int]
+    L.hxq_set_weights_on_stream.restype = None
+    L.hxq_set_weights_on_stream.argtypes = [C.c_int]
     L.hxq_dequant.restype = C.c_int
     L.hxq_dequant.argtypes = [P, C.c_int32, C.c_int32, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
     L.hxq_gemv_workspace_bytes.restype = C.c_size_t
@@ -104,8 +106,26 @@ def lib() -> C.CDLL:
     L.hxq_allreduce_oneshot.restype = C.c_int
     L.hxq_allreduce_oneshot.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
                                         C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+    L.hxq_allreduce_add_rmsnorm.restype = C.c_int
+    L.hxq_allreduce_add_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,
+                                            C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_float,
+                                            C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
     _lib = L
     return L
+
+
+class weights_on_stream:
+    """``with weights_on_stream():`` around a product whose descriptor buffers (codebook, indices,
+    scales, sidecar) were produced by kernels still in flight on the current stream: the decode
+    kernels then start only after those kernels have finished (see include/hxq_b200.h)."""
+
+    def __enter__(self):
+        lib().hxq_set_weights_on_stream(1)
+        return self
+
+    def __exit__(self, *exc):
+        lib().hxq_set_weights_on_stream(0)
+        return False
 
 
 def strerror(status: int) -> str:

@@ -106,6 +106,127 @@ __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const Peers
     }
 }
 
+
+// The same exchange with what follows it in a decoder layer folded in: after the sum over ranks the
+// row is added to the residual stream and RMS-normalised for the next projection,
+//     delta = bf16(sum_p partial_p);  h = bf16(h + delta);  out = bf16(bf16(h * rsqrt(mean(h^2) + eps)) * w),
+// rounded exactly where the separate kernels (hxq_allreduce_oneshot, then hxq_add_rmsnorm) round, so
+// the fused step is bit-identical to the unfused one.  One CTA owns whole rows (row r goes to CTA
+// r mod gridDim.x; H <= 8192) because the norm needs the whole row; flags, slots and call numbers
+// work as above, one flag per CTA covering all of its rows.
+constexpr int kRowMaxH = kThreads * 8 * 2;
+
+__global__ void __launch_bounds__(kThreads) allreduce_add_rmsnorm_kernel(
+    const Peers peers, int rank, int world, int64_t n_max, const float* __restrict__ src, int M, int H,
+    __nv_bfloat16* __restrict__ h, int64_t ld_h, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+    int64_t ld_out, float eps, uint32_t* __restrict__ counters, long long wait_cycles, int32_t* __restrict__ status) {
+    __shared__ uint32_t epoch_s;
+    __shared__ int ok_s;
+    __shared__ float red[kThreads / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // src and h are earlier kernels' outputs
+    const int cta = blockIdx.x, t = threadIdx.x, G = gridDim.x;
+    if (t == 0) {
+        epoch_s = counters[cta] + 1u;
+        counters[cta] = epoch_s;
+        ok_s = 1;
+    }
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    const int slot = (int)(epoch & 1u);
+
+    // push this rank's partial rows into slot [rank] of every rank's buffer (its own included)
+    for (int r = cta; r < M; r += G) {
+        for (int c0 = t * 8; c0 < H; c0 += kThreads * 8) {
+            const int64_t i0 = (int64_t)r * H + c0;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = (c0 + e < H) ? src[i0 + e] : 0.f;
+            for (int p = 0; p < world; ++p) {
+                float* d = peers.buf[p] + ((int64_t)slot * world + rank) * n_max + i0;
+                if (c0 + 8 <= H && (i0 & 3) == 0) {
+                    *reinterpret_cast<float4*>(d) = make_float4(v[0], v[1], v[2], v[3]);
+                    *reinterpret_cast<float4*>(d + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        if (c0 + e < H) d[e] = v[e];
+                }
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (t < world) {
+        volatile uint32_t* f = peers.flag[t] + ((int64_t)slot * world + rank) * kMaxCtas + cta;
+        *f = epoch;
+    }
+    if (t < world) {
+        volatile uint32_t* f = peers.flag[rank] + ((int64_t)slot * world + t) * kMaxCtas + cta;
+        const long long t0 = clock64();
+        while (*f != epoch) {
+            if (clock64() - t0 > wait_cycles) { ok_s = 0; break; }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (!ok_s) {
+        if (t == 0 && status != nullptr) atomicExch(status, HXQ_E_TIMEOUT);
+        return;
+    }
+    for (int r = cta; r < M; r += G) {
+        float hv[2][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c0 = t * 8 + j * kThreads * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) hv[j][e] = 0.f;
+            if (c0 < H) {
+                const float* base = peers.buf[rank] + (int64_t)slot * world * n_max + (int64_t)r * H + c0;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int p = 0; p < world; ++p) {   // fixed order: the same sum on every rank
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        if (c0 + e < H) acc[e] += __ldcg(base + (int64_t)p * n_max + e);
+                }
+                __nv_bfloat16* hp = h + (int64_t)r * ld_h + c0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    if (c0 + e < H) {
+                        const float delta = __bfloat162float(__float2bfloat16_rn(acc[e]));
+                        const __nv_bfloat16 hn = __float2bfloat16_rn(__bfloat162float(hp[e]) + delta);
+                        hp[e] = hn;
+                        hv[j][e] = __bfloat162float(hn);
+                        ss += hv[j][e] * hv[j][e];
+                    }
+                }
+            }
+        }
+        // block sum of squares
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        __syncthreads();                      // red[] from the previous row has been read by everyone
+        if ((t & 31) == 0) red[t >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int q = 0; q < kThreads / 32; ++q) tot += red[q];
+        const float rs = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c0 = t * 8 + j * kThreads * 8;
+            if (c0 < H) {
+                __nv_bfloat16* op = out + (int64_t)r * ld_out + c0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (c0 + e < H)
+                        op[e] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(hv[j][e] * rs)) * __bfloat162float(w[c0 + e]));
+            }
+        }
+    }
+}
+
 }  // namespace ar
 }  // namespace hxq
 
@@ -146,6 +267,40 @@ extern "C" int hxq_allreduce_oneshot(void* const* peer_buffers, void* const* pee
     const long long limit = wait_cycles > 0 ? (long long)wait_cycles : 2000000000LL;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, peers, (int)rank, (int)world, n_max,
                                              reinterpret_cast<const float*>(src), reinterpret_cast<__nv_bfloat16*>(dst), n,
+                                             reinterpret_cast<uint32_t*>(counters), limit, status);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+extern "C" int hxq_allreduce_add_rmsnorm(void* const* peer_buffers, void* const* peer_flags, int32_t rank, int32_t world,
+                                         int64_t n_max, const void* src, int32_t M, int32_t H, void* h, int64_t ld_h,
+                                         const void* weight, void* out, int64_t ld_out, float eps, void* counters,
+                                         int64_t wait_cycles, int32_t* status, hxq_stream_t stream) {
+    using namespace hxq::ar;
+    if (!peer_buffers || !peer_flags || !src || !h || !weight || !out || !counters) return HXQ_E_ARG;
+    if (world <= 0 || world > kMaxWorld || rank < 0 || rank >= world) return HXQ_E_ARG;
+    if (M <= 0 || H <= 0 || H > kRowMaxH || (int64_t)M * H > n_max || n_max % 8 != 0) return HXQ_E_SHAPE;
+    if (ld_h < H || ld_out < H) return HXQ_E_SHAPE;
+    Peers peers;
+    for (int p = 0; p < kMaxWorld; ++p) {
+        peers.buf[p] = p < world ? reinterpret_cast<float*>(peer_buffers[p]) : nullptr;
+        peers.flag[p] = p < world ? reinterpret_cast<uint32_t*>(peer_flags[p]) : nullptr;
+        if (p < world && (!peers.buf[p] || !peers.flag[p] || !hxq::aligned_to(peers.buf[p], 16))) return HXQ_E_ARG;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M < kMaxCtas ? M : kMaxCtas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const long long limit = wait_cycles > 0 ? (long long)wait_cycles : 2000000000LL;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel, peers, (int)rank, (int)world, n_max,
+                                             reinterpret_cast<const float*>(src), (int)M, (int)H,
+                                             reinterpret_cast<__nv_bfloat16*>(h), ld_h,
+                                             reinterpret_cast<const __nv_bfloat16*>(weight),
+                                             reinterpret_cast<__nv_bfloat16*>(out), ld_out, eps,
                                              reinterpret_cast<uint32_t*>(counters), limit, status);
     return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }

@@ -4,6 +4,12 @@
 
 extern "C" int hxq_version(void) { return HXQ_VERSION_NUMBER; }
 
+namespace hxq {
+thread_local int g_weights_on_stream = 0;
+}  // namespace hxq
+
+extern "C" void hxq_set_weights_on_stream(int on) { hxq::g_weights_on_stream = on ? 1 : 0; }
+
 extern "C" const char* hxq_strerror(int status) {
     switch (status) {
         case HXQ_OK: return "ok";

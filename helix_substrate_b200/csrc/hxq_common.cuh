@@ -12,6 +12,10 @@
 
 namespace hxq {
 
+// Set by hxq_set_weights_on_stream (per host thread): the decode kernels then launch without the
+// programmatic-dependent-launch attribute, i.e. only after everything before them in the stream is done.
+extern thread_local int g_weights_on_stream;
+
 // ---- element conversion ----------------------------------------------------
 template <int DT> struct Elem;
 template <> struct Elem<HXQ_F32> {

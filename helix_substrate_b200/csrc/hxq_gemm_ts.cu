@@ -52,6 +52,8 @@ constexpr int SMEM_TOTAL = 232448;
 constexpr int MAX_STAGES = 4;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COLS = KS / 2;                  // 64 columns of packed bf16 pairs per stage
+constexpr int kPrefetch = 10;                   // stages the L2 prefetch of index lines runs ahead
+static_assert((3 * MAX_STAGES + 1) * 8 + 8 <= 128, "barriers must fit the unused half of the table's first row");
 
 struct Args {
     const float* cb;
@@ -61,11 +63,12 @@ struct Args {
     const int32_t* cols;
     const float* deltas;
     const float* bias;
-    const __nv_bfloat16* xb;   // activations as bf16 [M, ldxb] (the sidecar reads them directly)
+    const uint8_t* idx;        // index matrix (for the L2 prefetches; the data itself comes through TMA)
+    int64_t ld_idx;
     void* y;
     int32_t* status;
     float* partial;            // [splits][M][out_features] when the K range is split, else nullptr
-    int64_t ldy, ldxb;
+    int64_t ldy;
     int32_t out_features, in_features, col0, group_size, ld_st, st_dtype, n_groups;
     int32_t M, y_dtype, k_steps, k_per_split;
 };
@@ -108,8 +111,7 @@ __device__ __forceinline__ void tmem_st_wait() {
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x,
-               const __grid_constant__ CUtensorMap map_pf, const Args a) {
+gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x, const Args a) {
     constexpr int B_BYTES = BN * KS * 2;                 // two [BN x 64] bf16 sub-tiles
     constexpr int STAGE_BYTES = IDX_BYTES + B_BYTES;     // multiple of 1024
     extern __shared__ __align__(1024) char smem_raw[];
@@ -153,7 +155,6 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
         sm100::fence_barrier_init();
         sm100::prefetch_tensormap(&map_idx);
         sm100::prefetch_tensormap(&map_x);
-        sm100::prefetch_tensormap(&map_pf);
     }
     if (warp == 1) {
         sm100::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -173,23 +174,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
     } else if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            // A stage's index box is 128 bytes of each of 128 rows: fetched like that from DRAM, every
-            // access would open a page for 128 bytes.  So the same rows are pulled into L2 ahead of time
-            // in boxes four stages (512 bytes per row) wide, and the stage loads then hit L2.
-            auto prefetch_box = [&](int ks4) {     // ks4: first stage of the box, relative to KS0
-                const int col = (KS0 + ks4) * KS;
-                if (ks4 < NK && col < a.in_features)
-                    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                                 :: "l"(reinterpret_cast<uint64_t>(&map_pf)), "r"(col / 4), "r"(o0) : "memory");
-            };
-            prefetch_box(0);
-            prefetch_box(4);
-            prefetch_box(8);
             int armed = 0;
             for (int ks = 0; ks < NK; ++ks) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-                if ((ks & 3) == 0) prefetch_box(ks + 12);
                 if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                 char* st = stage_ptr(s);
                 sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)STAGE_BYTES);
@@ -269,12 +257,26 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
         }
         float sc_n, of_n;
         load_st(0, sc_n, of_n);
+        if (kq == 0 && row_ok) {
+            for (int pk = 0; pk < kPrefetch && pk < NK; ++pk) {
+                const int64_t col = (int64_t)(KS0 + pk) * KS;
+                if (col < a.in_features) asm volatile("prefetch.global.L2 [%0];" :: "l"(a.idx + (int64_t)row * a.ld_idx + col));
+            }
+        }
         int done = 0;
         for (int ks = 0; ks < NK; ++ks) {
             const int s = ks % STAGES;
             const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
             const float sc = sc_n, of = of_n;
             if (ks + 1 < NK) load_st(ks + 1, sc_n, of_n);
+            // A stage's index box is one 128-byte line of each of 128 rows, and an SM's bulk-copy unit
+            // keeps too few such lines in flight to cover DRAM latency.  So the row's line of a stage
+            // kPrefetch ahead is asked into L2 now (one thread per row and stage; nothing comes back).
+            if (kq == 0 && row_ok && ks + kPrefetch < NK) {
+                const int64_t col = (int64_t)(KS0 + ks + kPrefetch) * KS;
+                if (col < a.in_features)
+                    asm volatile("prefetch.global.L2 [%0];" :: "l"(a.idx + (int64_t)row * a.ld_idx + col));
+            }
             if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
             const uint32_t idx_row = sm100::smem_u32(stage_ptr(s)) + (uint32_t)(r * 128);
             uint32_t out[16];
@@ -433,8 +435,8 @@ size_t split_bytes(const hxq_desc* d, int32_t M) {
 }
 
 template <int BN>
-static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const CUtensorMap& mp, const Args& a, int grid_m, int grid_o,
-                  int splits, cudaStream_t stream) {
+static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, int grid_m, int grid_o, int splits,
+                  cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -443,7 +445,7 @@ static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const CUtensorMa
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mi, mx, mp, a);
+    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mi, mx, a);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
@@ -459,15 +461,10 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
     if (!gemm::make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, (uint64_t)d->in_features, (uint64_t)M,
                            (uint64_t)ldxb * 2, 64, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return HXQ_E_DEVICE;
-    // the same index matrix as 32-bit words, in boxes of 512 bytes x 128 rows: L2 prefetches only
-    CUtensorMap mp;
-    if (!gemm::make_map_2d(&mp, CU_TENSOR_MAP_DATA_TYPE_UINT32, d->indices, (uint64_t)d->in_features / 4,
-                           (uint64_t)d->out_features, (uint64_t)d->ld_idx, 128, BM, CU_TENSOR_MAP_SWIZZLE_NONE))
-        return HXQ_E_DEVICE;
     Args a;
     a.cb = d->codebook; a.scales = d->scales; a.offsets = d->offsets;
     a.rowptr = d->rowptr; a.cols = d->cols; a.deltas = d->deltas; a.bias = d->bias;
-    a.xb = xb; a.ldxb = ldxb;
+    a.idx = d->indices; a.ld_idx = d->ld_idx;
     a.y = y; a.status = status_word; a.ldy = ldy;
     a.out_features = d->out_features; a.in_features = d->in_features; a.col0 = d->col0;
     a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
@@ -488,10 +485,10 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
         splits = 1;
     }
     int st;
-    if (BN == 128) st = launch<128>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
-    else if (BN == 64) st = launch<64>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
-    else if (BN == 32) st = launch<32>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
-    else st = launch<16>(mi, mx, mp, a, grid_m, grid_o, splits, stream);
+    if (BN == 128) st = launch<128>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 64) st = launch<64>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 32) st = launch<32>(mi, mx, a, grid_m, grid_o, splits, stream);
+    else st = launch<16>(mi, mx, a, grid_m, grid_o, splits, stream);
     if (st != HXQ_OK || splits == 1) return st;
     gemm::launch_splitk_reduce(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy, stream);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;

@@ -1198,7 +1198,7 @@ static cudaLaunchConfig_t gemv_launch_config(const GemvPlan& p, int smem_bytes, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up may overlap the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_weights_on_stream ? 0 : 1;   // weights still being written on this stream: no early start
     return cfg;
 }
 

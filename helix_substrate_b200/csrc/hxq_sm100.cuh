@@ -39,15 +39,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is
+// pending: a waiting warp then issues (almost) nothing instead of spinning through the scheduler.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait: gives up after `limit` clock cycles or as soon as another thread
 // of the CTA has given up (*abort != 0); on giving up it raises *abort itself.
-// Returns false when the wait did not complete.
+// Returns false when the wait did not complete.  While the phase is pending the thread sleeps in
+// the barrier unit (a few microseconds per try), so waiting warps leave the issue slots to the
+// warps that work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
                                           long long limit = 2000000000LL) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
         if (*abort != 0) return false;
         if (clock64() - t0 > limit) {
             *abort = 1;

@@ -46,6 +46,10 @@ def _workspace(device: torch.device, nbytes: int, kind: str = "gemv") -> Optiona
     key = (device.index, torch.cuda.current_stream(device).cuda_stream, kind)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                "hxq kernels need their scratch buffer of this stream allocated (and zeroed) before a CUDA graph "
+                "capture starts: run the step once on the capturing stream first, then capture")
         ws = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws

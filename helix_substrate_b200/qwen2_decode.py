@@ -154,8 +154,8 @@ def run_ranks_in_process(gens):
         raise RuntimeError("a rank finished before its first exchange")
     while True:
         total = items[0][0].float().clone()
-        for part, _ in items[1:]:
-            total += part.float()
+        for it in items[1:]:
+            total += it[0].float()
         total = total.to(torch.bfloat16)
         nxt, done = [], 0
         for r, g in enumerate(gens):
@@ -216,7 +216,7 @@ class Qwen2HxqDecoder(nn.Module):
         """ids [B, T]; positions [T] (absolute); the new K/V go to cache rows
         ``cache_rows`` [T]; attention spans cache[:attn_len] (None = whole cache
         with a position mask, which is what the captured one-token step uses)."""
-        return _drive(self.blocks_tokens(ids, positions, cache_rows, attn_len), lambda part, key: self._allreduce(part))
+        return _drive(self.blocks_tokens(ids, positions, cache_rows, attn_len), lambda part, key, *_: self._allreduce(part))
 
     def blocks_tokens(self, ids: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor,
                       attn_len: Optional[int]):
@@ -271,11 +271,14 @@ class Qwen2HxqDecoder(nn.Module):
             self._sb = sb
         return sb
 
-    def _reduce_step(self, part: torch.Tensor, key: str) -> torch.Tensor:
-        """Sum of one step's row-parallel partial over the ranks, bf16 result in the step buffer ``key``."""
+    def _reduce_step(self, part: torch.Tensor, key: str, w_next: torch.Tensor = None):
+        """Sum of one step's row-parallel partial over the ranks.  With the one-shot kernel the residual
+        add and the next RMSNorm are folded into the same launch (h and x of the step buffers are
+        updated in place) and None is returned; otherwise the bf16 sum is."""
         sb = self._sb
         if self.p2p:
-            return self._ar(part, out=sb[key])
+            self._ar.add_rmsnorm(part, sb["h"], w_next, self.shp.rms_eps, sb["x"])
+            return None
         return self._allreduce(part)
 
     def step_fused(self, tok: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
@@ -294,7 +297,6 @@ class Qwen2HxqDecoder(nn.Module):
         bf = torch.bfloat16
         h, x = sb["h"], sb["x"]
         h.copy_(self.embed[tok[:, 0]])
-        delta = None
 
         def row_parallel(lin, xin, key):
             if fp32_partials:
@@ -303,9 +305,10 @@ class Qwen2HxqDecoder(nn.Module):
                 return lin.packed().matmul(xin, torch.float32, out=sb["p32"]), key
             return lin.packed().matmul(xin, bf, out=sb[key]), key
 
+        n_layers = len(self.layers)
+        decode_ops.add_rmsnorm(h, None, self.layers[0].ln1, eps, x)
         for li, L in enumerate(self.layers):
             nq, nkv = L.n_q, L.n_kv
-            decode_ops.add_rmsnorm(h, delta, L.ln1, eps, x)
             qkv, gu, ni = sb["qkv"], sb["gu"], L.inter_local
             if L.fused:
                 L.qkv_proj.packed().matmul(x, bf, out=qkv)
@@ -315,16 +318,21 @@ class Qwen2HxqDecoder(nn.Module):
                 L.v_proj.packed().matmul(x, bf, out=qkv[:, (nq + nkv) * D:])
             decode_ops.rope_append(qkv, pos, self.cos, self.sin, sb["q"], self.k_cache[li], self.v_cache[li], nq, nkv)
             decode_ops.attn_decode(sb["q"], self.k_cache[li], self.v_cache[li], pos, sb["a"], nq, D ** -0.5)
-            delta = yield row_parallel(L.o_proj, sb["a"], "d1")
-            decode_ops.add_rmsnorm(h, delta, L.ln2, eps, x)
+            # the exchange is handed the weight of the norm that follows it: a driver that folds the
+            # residual add and that norm into the sum answers None
+            delta = yield (*row_parallel(L.o_proj, sb["a"], "d1"), L.ln2)
+            if delta is not None:
+                decode_ops.add_rmsnorm(h, delta, L.ln2, eps, x)
             if L.fused:
                 L.gate_up_proj.packed().matmul(x, bf, out=gu)
             else:
                 L.gate_proj.packed().matmul(x, bf, out=gu[:, :ni])
                 L.up_proj.packed().matmul(x, bf, out=gu[:, ni:])
             decode_ops.swiglu(gu[:, :ni], gu[:, ni:], sb["act"])
-            delta = yield row_parallel(L.down_proj, sb["act"], "d2")
-        decode_ops.add_rmsnorm(h, delta, self.norm, eps, x)
+            w_next = self.layers[li + 1].ln1 if li + 1 < n_layers else self.norm
+            delta = yield (*row_parallel(L.down_proj, sb["act"], "d2"), w_next)
+            if delta is not None:
+                decode_ops.add_rmsnorm(h, delta, w_next, eps, x)
         return x @ self.lm_head.t()
 
     @torch.no_grad()

@@ -258,6 +258,28 @@ class OneShotAllReduce:
         _lib.check(st, "hxq_allreduce_oneshot")
         return out
 
+    def add_rmsnorm(self, partial: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, eps: float,
+                    out: torch.Tensor) -> torch.Tensor:
+        """The sum over ranks of ``partial`` [M, H] (fp32) added to the residual stream ``h`` in place
+        and RMS-normalised into ``out`` (both bf16 [M, H]) - ``hxq_allreduce_add_rmsnorm``, bit-identical
+        to ``self(partial)`` followed by ``decode_ops.add_rmsnorm``.  An object used for this call must not
+        also be used for plain sums (one CTA owns rows here, 4096-element slices there)."""
+        import ctypes as C
+        from . import _lib
+        assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous() and partial.ndim == 2
+        M, H = partial.shape
+        for t in (h, out):
+            assert t.dtype == torch.bfloat16 and t.shape == (M, H) and t.stride(1) == 1
+        assert weight.dtype == torch.bfloat16 and weight.numel() == H and weight.is_contiguous()
+        with torch.cuda.device(self.device):
+            st = _lib.lib().hxq_allreduce_add_rmsnorm(
+                self._bufs, self._flags, self.rank, self.world, self.n_max, C.c_void_p(partial.data_ptr()), M, H,
+                C.c_void_p(h.data_ptr()), h.stride(0), C.c_void_p(weight.data_ptr()), C.c_void_p(out.data_ptr()),
+                out.stride(0), float(eps), C.c_void_p(self.counters.data_ptr()), self.wait_cycles,
+                C.c_void_p(self.status.data_ptr()), C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        _lib.check(st, "hxq_allreduce_add_rmsnorm")
+        return out
+
     def check_status(self) -> int:
         """0, or HXQ_E_TIMEOUT if a rank gave up waiting for the others (synchronises)."""
         return int(self.status.item())

@@ -41,7 +41,9 @@ def fused_affine_group_matmul(x: torch.Tensor, indices: torch.Tensor, scales: to
     """Y[n, o] = sum_i X[n, i] * (indices[o, i] * scale[o, i//G] + offset[o, i//G]) (+ bias), fp32."""
     assert x.is_cuda and indices.is_cuda
     assert x.ndim == 2 and indices.ndim == 2 and indices.shape[1] == x.shape[1]
-    return _weight(indices, scales, offsets, group_size, bias).matmul(x, out_dtype=torch.float32)
+    from . import _lib
+    with _lib.weights_on_stream():   # dtype conversions / index expansion may still be in flight on this stream
+        return _weight(indices, scales, offsets, group_size, bias).matmul(x, out_dtype=torch.float32)
 
 
 def unpack6(packed: torch.Tensor, out_features: int, in_features: int) -> torch.Tensor:

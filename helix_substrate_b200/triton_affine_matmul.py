@@ -30,7 +30,9 @@ def fused_affine_matmul(x: torch.Tensor, indices: torch.Tensor, step: float, off
     assert x.shape[1] == indices.shape[1], f"IN mismatch: {x.shape[1]} vs {indices.shape[1]}"
     assert indices.dtype == torch.uint8, "Expected uint8 indices"
     w = HxqWeight(_codebook(step, offset, indices.device), indices.contiguous(), bias=bias)
-    return w.matmul(x, out_dtype=torch.float32)
+    from . import _lib
+    with _lib.weights_on_stream():   # the ramp codebook is computed per call on this stream
+        return w.matmul(x, out_dtype=torch.float32)
 
 
 def affine_matmul_reference(x: torch.Tensor, indices: torch.Tensor, step: float, offset: float,

@@ -118,7 +118,8 @@ def fused_vq_matmul(
     idx = indices if indices.stride(1) == 1 else indices.contiguous()
     w = HxqWeight(cb.contiguous(), idx, bias=bias, **kw)
     try:
-        out = w.matmul(x, out_dtype=torch.float32)
+        with _lib.weights_on_stream():   # the CSR / deltas / padded codebook above were made on this stream
+            out = w.matmul(x, out_dtype=torch.float32)
     except _lib.HxqError as e:
         raise RuntimeError(f"hxq kernel launch failed: {e}. N={N}, IN={IN}, OUT={OUT}. No silent fallback.") from e
     if _dispatch_log is not None:

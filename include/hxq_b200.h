@@ -76,6 +76,18 @@ typedef struct hxq_desc {
 /* Library version as major*10000 + minor*100 + patch. */
 int hxq_version(void);
 
+/*
+ * hxq_gemv / hxq_gemv_static start their set-up (codebook table, first index rows, scale / offset /
+ * row-pointer reads) BEFORE the kernels in front of them on the stream have finished (programmatic
+ * dependent launch) and only wait for those kernels before they touch x, y and the workspace.
+ * PRECONDITION: every buffer named in the hxq_desc is complete before the call is enqueued - which
+ * is the case for weights loaded once.  A caller that produces a descriptor's buffers with kernels
+ * on the SAME stream right before the product (a codebook computed per call, indices unpacked per
+ * call) brackets the call with hxq_set_weights_on_stream(1) ... (0): while set (per host thread),
+ * the products launch as ordinary stream-ordered kernels.  No counterpart in the reference.
+ */
+void hxq_set_weights_on_stream(int on);
+
 /* Static, human-readable text for a status code. */
 const char* hxq_strerror(int status);
 
@@ -238,6 +250,20 @@ size_t hxq_allreduce_flag_bytes(int32_t world);
 int hxq_allreduce_oneshot(void* const* peer_buffers, void* const* peer_flags, int32_t rank, int32_t world,
                           int64_t n_max, const void* src, void* dst, int64_t n, void* counters,
                           int64_t wait_cycles, int32_t* status, hxq_stream_t stream);
+
+/*
+ * hxq_allreduce_oneshot with the next two steps of a decoder layer folded in (same buffers, flags,
+ * counters, bounded wait and status word; no counterpart in the reference): after the sum over
+ * ranks of src [M, H] (fp32 partials of a row-parallel o_proj / down_proj),
+ *     delta = bf16(sum);   h[m, :] = bf16(h + delta);   out[m, :] = rmsnorm(h[m, :], eps) * weight
+ * rounded exactly where hxq_allreduce_oneshot followed by hxq_add_rmsnorm round.  h, out: bf16
+ * [M, ld]; weight: bf16 [H]; H <= 8192; M * H <= n_max.  One CTA owns whole rows, so calls of this
+ * entry point and of hxq_allreduce_oneshot must not share one set of buffers / flags / counters.
+ */
+int hxq_allreduce_add_rmsnorm(void* const* peer_buffers, void* const* peer_flags, int32_t rank, int32_t world,
+                              int64_t n_max, const void* src, int32_t M, int32_t H, void* h, int64_t ld_h,
+                              const void* weight, void* out, int64_t ld_out, float eps, void* counters,
+                              int64_t wait_cycles, int32_t* status, hxq_stream_t stream);
 
 /*
  * Host helper: CSR row pointer from ascending flat positions

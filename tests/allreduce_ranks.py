@@ -48,12 +48,33 @@ def main():
         torch.cuda.synchronize()
         assert (out.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3
     assert ar.check_status() == 0
+    # the same exchange with the residual add and the RMSNorm folded in, against NCCL + the separate operator
+    from helix_substrate_b200 import decode_ops
+    M, H = 4, 3584
+    ar2 = OneShotAllReduce(M * H, dev)
+    w = (1.0 + 0.1 * torch.randn(H, device=dev, generator=torch.Generator(device=dev).manual_seed(5))).bfloat16()
+    h = torch.randn(M, H, device=dev, generator=torch.Generator(device=dev).manual_seed(6)).bfloat16()
+    h_ref = h.clone()
+    for it in range(5):
+        part = torch.randn(M, H, device=dev, generator=g)
+        x = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+        ar2.add_rmsnorm(part, h, w, 1e-6, x)
+        tot = part.clone()
+        dist.all_reduce(tot)
+        x_ref = torch.empty_like(x)
+        decode_ops.add_rmsnorm(h_ref, tot.bfloat16(), w, 1e-6, x_ref)
+        assert (h.float() - h_ref.float()).abs().max().item() <= 0.02 * h_ref.float().abs().max().item() + 1e-3, it
+        assert (x.float() - x_ref.float()).abs().max().item() <= 0.05 * x_ref.float().abs().max().item() + 1e-3, it
+        h_ref.copy_(h)     # the two sums may differ in the last bit (fixed rank order vs NCCL's): keep them in step
+    assert ar2.check_status() == 0
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
         print("ALLREDUCE-OK", flush=True)
     sys.stdout.flush()
-    os._exit(0)   # no process-group teardown while a captured graph is alive
+    del graph
+    from helix_substrate_b200.qwen2_decode import leave_process_group
+    leave_process_group()
 
 
 if __name__ == "__main__":

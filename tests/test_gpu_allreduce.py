@@ -58,6 +58,45 @@ def test_sum_in_rank_order_with_the_other_ranks_played_by_the_test(world, rank, 
     assert ar.check_status() == 0
 
 
+@pytest.mark.parametrize("world,rank,M,H", [(1, 0, 1, 3584), (2, 1, 1, 3584), (4, 2, 3, 3584), (8, 5, 40, 5120), (2, 0, 5, 264)])
+def test_sum_with_residual_add_and_rmsnorm_folded_in(world, rank, M, H):
+    """hxq_allreduce_add_rmsnorm against the two separate operators it replaces, bit for bit, with the
+    other ranks played by the test (one CTA owns whole rows: min(M, 32) flags per source rank)."""
+    from helix_substrate_b200 import decode_ops
+    from helix_substrate_b200.tp import OneShotAllReduce
+    dev = _dev()
+    n = M * H
+    fused = OneShotAllReduce.local_emulation(world, rank, n, dev)
+    plain = OneShotAllReduce.local_emulation(world, rank, n, dev)
+    g = torch.Generator(device=dev).manual_seed(world * 1000 + M)
+    w = (1.0 + 0.1 * torch.randn(H, device=dev, generator=g)).bfloat16()
+    h_f = torch.randn(M, H, device=dev, generator=g).bfloat16()
+    h_p = h_f.clone()
+    n_cta_rows, n_cta_flat = min(M, 32), -(-n // 4096)
+    for call in (1, 2, 3):
+        slot = call & 1
+        parts = [torch.randn(M, H, device=dev, generator=g) for _ in range(world)]
+        for ar, n_cta in ((fused, n_cta_rows), (plain, n_cta_flat)):
+            data, flags = ar.views()
+            for p in range(world):
+                if p != rank:
+                    data[slot, p, :n] = parts[p].reshape(-1)
+                    flags[slot, p, :n_cta] = call
+        torch.cuda.synchronize()
+        x_f = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+        fused.add_rmsnorm(parts[rank], h_f, w, 1e-6, x_f)
+        delta = plain(parts[rank].reshape(-1)).view(M, H)
+        x_p = torch.empty_like(x_f)
+        decode_ops.add_rmsnorm(h_p, delta, w, 1e-6, x_p)
+        assert torch.equal(h_f, h_p), f"call {call}: residual stream"
+        assert torch.equal(x_f, x_p), f"call {call}: normalised row"
+        for p in range(world):   # the push reached every rank's buffer, with the flags of all row CTAs
+            d, f = fused.views(p)
+            assert torch.equal(d[slot, rank, :n], parts[rank].reshape(-1))
+            assert bool((f[slot, rank, :n_cta_rows] == call).all())
+    assert fused.check_status() == 0
+
+
 def test_a_wait_that_runs_out_reports_and_leaves_the_context_usable():
     from helix_substrate_b200 import _lib
     from helix_substrate_b200.tp import OneShotAllReduce

@@ -116,6 +116,9 @@ SHAPES = [  # (OUT, IN, G, col0)
     (8, 512, 0, 0), (50, 528, 0, 0), (64, 1024, 128, 0), (100, 3584, 128, 0), (37, 2064, 128, 0),
     (72, 448, 128, 448), (40, 2368, 128, 2368 * 3), (16, 1536, 256, 0), (24, 1536, 1536, 0),
     (300, 160, 32, 0), (19, 77, 0, 0),
+    # whole 128-column groups but a short last 512-column chunk: the streaming kernel masks lanes
+    # (the shapes of group-aligned tensor-parallel shards: 18944 / 8 -> 2432, 13824 / 8 -> 1792)
+    (64, 1792, 128, 0), (24, 640, 128, 0), (40, 2432, 128, 2432), (16, 128, 128, 0), (32, 896, 0, 0),
 ]
 
 
