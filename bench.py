@@ -419,7 +419,7 @@ def main():
 
     if args.workload in ("prefill", "decode"):
         if args.workload == "prefill":
-            blk = block_prefill([args.m if args.m > 16 else 2048], dev, max(args.block_seconds, 2.0))
+            blk = block_prefill([args.m if args.m > 16 else 2048], dev, args.block_seconds)
             val, unit, metric = blk["by_m"][0]["TFLOPs"], "TFLOP/s", "hxq_prefill_gemm_TFLOPS_qwen2.5-7b_projections"
         else:
             blk = block_decode(dev, rank, world, [args.batch], allreduce=args.allreduce)

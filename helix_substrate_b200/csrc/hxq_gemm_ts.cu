@@ -1,30 +1,43 @@
-// hxq_gemm, 17 .. 128 tokens: y[m, o] = sum_i x[m, i] * W^[o, i] + sidecar + bias on the tensor cores
+// hxq_gemm, 5 .. 128 tokens: y[m, o] = sum_i x[m, i] * W^[o, i] + sidecar + bias on the tensor cores
 // with the dequantised weights handed to the MMA through TENSOR MEMORY, never through shared memory.
 //
 // At these token counts the product is still bound by the index stream (one byte and one table lookup
 // per weight, each weight used for at most 128 tokens), so the kernel is built like the decode kernel,
-// not like a GEMM: everything that is not a lookup is kept off the shared-memory data path.
+// not like a GEMM: everything that is not a lookup is kept off the instruction stream of the warps
+// that do the lookups.
 //
 //   * CTA tile: 128 output rows x BN tokens (BN = 16, 32, 64, 128), K walked in stages of 128 columns,
 //     one CTA per SM; small row-tile grids split K over gridDim.z (fp32 partials + a fixed-order sum).
-//   * warp 0, one lane: TMA producer.  Per stage one 128 x 128 box of index bytes and two 64-column
-//     boxes of bf16 activations, all 128-byte swizzled, on one mbarrier.  No multicast, no cluster.
+//   * index bytes: the 512 dequantising threads copy each stage's 128 x 128 box themselves with two
+//     16-byte asynchronous copies per thread (eight lanes per 128-byte line: whole lines per request)
+//     into a ring of up to eight 16 KB boxes laid out in the 128-byte swizzle, up to seven stages
+//     (112 KB per SM) ahead: that much in flight is what this access pattern needs to run near the
+//     DRAM rate.  Each thread's copies report to the box's mbarrier (cp.async.mbarrier.arrive); a
+//     second barrier per box, one arrival per warp, says the codes are in registers and the box may
+//     be refilled.  The warps are not otherwise synchronised: one named barrier per stage over all
+//     512 threads instead was 15 % slower (every stage then takes as long as its slowest warp).
+//   * scale and offset: the 128 rows' values for four stages at a time ride with the index copies
+//     (one 16-byte copy per row and table) into the unused halves of the codebook table's rows.
+//   * warp 0, one lane: TMA producer of the activation tiles (two 64-column boxes of bf16 per stage,
+//     128-byte swizzled, ring of three to six).  No multicast, no cluster.
 //   * warps 2..17: dequantisers, ONE THREAD PER OUTPUT ROW and 32-column quarter of the stage.  A
 //     thread reads its row's 32 codes with two conflict-free 16-byte loads (the swizzle spreads eight
 //     rows over all banks), looks each up in the lane-replicated codebook (one byte-permute + one
 //     load per weight, bank == lane), applies its (row, group) scale and offset in fp32, adds the
 //     row's sidecar deltas that fall into its columns, packs pairs to bf16 and stores its 16
 //     registers straight into the A operand's columns of tensor memory (tcgen05.st 32x32b: TMEM
-//     lane == output row).  Scale/offset and the sidecar cursor are thread-local: there is no
-//     cross-lane step anywhere.
+//     lane == output row).  The store of a stage is waited for after the lookups of the next one.
+//     The sidecar cursor is thread-local: no cross-lane step anywhere.  (Adding the sidecar term in
+//     the epilogue instead - delta times the activation at its column, per token - was tried: every
+//     such load is a cache-line look-up per lane, 13 us per tile at 32 tokens and 44 us at 128.)
 //   * warp 1, one lane: issues tcgen05.mma kind::f16 with A from tensor memory and B (activations,
 //     K-major, 128-byte swizzle) from shared memory into the fp32 accumulator in tensor memory, and
-//     commits the stage back to the producer.
+//     commits the stage, which frees its activation tile and its A columns.
 //   * epilogue (the dequantising warps): accumulator -> registers, + bias, store.
 //
 // Every mbarrier wait is clock-bounded; a wait that gives up raises a CTA-wide abort flag and the
-// global status word (HXQ_E_TIMEOUT), in-flight copies are given time to land and tensor memory is
-// freed before the CTA returns.
+// global status word (HXQ_E_TIMEOUT); every other wait of the CTA then returns at its next poll,
+// in-flight copies are waited for and tensor memory is freed before the CTA returns.
 
 #include <cuda.h>
 #include <stdlib.h>
@@ -45,15 +58,13 @@ namespace gemmts {
 constexpr int BM = 128;             // output rows per CTA = UMMA M = TMEM lanes
 constexpr int KS = 128;             // K columns per stage
 constexpr int DEQ_WARPS = 16;       // four warps per TMEM lane quarter, each takes 32 of a stage's 128 columns
-constexpr int NUM_THREADS = 32 * (2 + DEQ_WARPS);
+constexpr int DEQ_THREADS = 32 * DEQ_WARPS;
+constexpr int NUM_THREADS = 32 * (2 + DEQ_WARPS);   // activation producer, MMA issuer, 16 dequantisers
 constexpr int LUT_BYTES = 256 * 256;            // entry c, lane l at c * 256 + l * 4, base on a 64 KB boundary
 constexpr int IDX_BYTES = BM * KS;              // 16 KB
 constexpr int SMEM_TOTAL = 232448;
-constexpr int MAX_STAGES = 4;
 constexpr int TMEM_COLS = 512;
 constexpr int A_COLS = KS / 2;                  // 64 columns of packed bf16 pairs per stage
-constexpr int kPrefetch = 10;                   // stages the L2 prefetch of index lines runs ahead
-static_assert((3 * MAX_STAGES + 1) * 8 + 8 <= 128, "barriers must fit the unused half of the table's first row");
 
 struct Args {
     const float* cb;
@@ -63,7 +74,7 @@ struct Args {
     const int32_t* cols;
     const float* deltas;
     const float* bias;
-    const uint8_t* idx;        // index matrix (for the L2 prefetches; the data itself comes through TMA)
+    const uint8_t* idx;        // index matrix [out_features, ld_idx]
     int64_t ld_idx;
     void* y;
     int32_t* status;
@@ -108,34 +119,52 @@ __device__ __forceinline__ uint32_t add_to_half(uint32_t pair, int hi, float del
 __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// Ring depths per token tile: NB activation tiles / A-operand column blocks, NI index boxes.  The
+// table sits on a 64 KB boundary of the shared window, which leaves ~63 KB below and ~100 KB above it.
+template <int BN> struct Rings;
+template <> struct Rings<16> { static constexpr int NB = 6, NI = 8; };
+template <> struct Rings<32> { static constexpr int NB = 5, NI = 7; };
+template <> struct Rings<64> { static constexpr int NB = 4, NI = 5; };
+template <> struct Rings<128> { static constexpr int NB = 3, NI = 3; };
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x, const Args a) {
+gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
     constexpr int B_BYTES = BN * KS * 2;                 // two [BN x 64] bf16 sub-tiles
-    constexpr int STAGE_BYTES = IDX_BYTES + B_BYTES;     // multiple of 1024
+    constexpr int NB = Rings<BN>::NB;
+    constexpr int NI = Rings<BN>::NI;
+    constexpr int PD = NI - 1;                           // stages the index copies run ahead
+    static_assert((BN < 32 ? 32 : BN) + NB * A_COLS <= TMEM_COLS, "accumulator + A ring must fit tensor memory");
+    static_assert(NI >= 2 && NI <= 8 && NB >= 2 && NB <= 6, "barrier and slot-table layout");
     extern __shared__ __align__(1024) char smem_raw[];
     const uint32_t smem_base = sm100::smem_u32(smem_raw);
     const uint32_t lut_base = (smem_base + 0xFFFFu) & ~0xFFFFu;
-    // stages: as many as fit below the table, the rest above it
+    char* lut = smem_raw + (lut_base - smem_base);
+    // Two rings share what is left of shared memory around the table: the larger items first, below
+    // the table while they fit there, then the smaller ones in what is left below, the rest above.
     const uint32_t lo0 = (smem_base + 1023u) & ~1023u;
     const uint32_t hi0 = lut_base + LUT_BYTES;
-    const int n_lo = (int)((lut_base - lo0) / STAGE_BYTES);
-    const int n_hi = (int)((smem_base + SMEM_TOTAL - hi0) / STAGE_BYTES);
-    const int STAGES = (n_lo + n_hi) < MAX_STAGES ? (n_lo + n_hi) : MAX_STAGES;
-    auto stage_ptr = [&](int s) -> char* {
-        const uint32_t addr = s < n_lo ? lo0 + (uint32_t)s * STAGE_BYTES : hi0 + (uint32_t)(s - n_lo) * STAGE_BYTES;
-        return smem_raw + (addr - smem_base);
-    };
-    char* lut = smem_raw + (lut_base - smem_base);
-    // barriers live in the unused upper half of the table's first row
-    uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 128);
-    uint64_t* tma_full = bars;                       // [MAX_STAGES] index + activation bytes landed
-    uint64_t* a_full = bars + MAX_STAGES;            // [MAX_STAGES] A columns of the stage written
-    uint64_t* empty = bars + 2 * MAX_STAGES;         // [MAX_STAGES] MMAs of the stage retired
-    uint64_t* acc_full = bars + 3 * MAX_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * MAX_STAGES + 1);
+    constexpr bool B_FIRST = B_BYTES > IDX_BYTES;
+    constexpr uint32_t SZ1 = B_FIRST ? B_BYTES : IDX_BYTES, SZ2 = B_FIRST ? IDX_BYTES : B_BYTES;
+    constexpr int N1 = B_FIRST ? NB : NI, N2 = B_FIRST ? NI : NB;
+    const int room_lo = (int)(lut_base - lo0);
+    const int n1_lo = room_lo / (int)SZ1 < N1 ? room_lo / (int)SZ1 : N1;
+    const int n2_lo = (room_lo - n1_lo * (int)SZ1) / (int)SZ2 < N2 ? (room_lo - n1_lo * (int)SZ1) / (int)SZ2 : N2;
+    const uint32_t lo2 = lo0 + (uint32_t)n1_lo * SZ1, hi2 = hi0 + (uint32_t)(N1 - n1_lo) * SZ1;
+    const bool layout_ok = hi2 + (uint32_t)(N2 - n2_lo) * SZ2 <= smem_base + SMEM_TOTAL;
+    auto slot1 = [&](int i) -> uint32_t { return i < n1_lo ? lo0 + (uint32_t)i * SZ1 : hi0 + (uint32_t)(i - n1_lo) * SZ1; };
+    auto slot2 = [&](int i) -> uint32_t { return i < n2_lo ? lo2 + (uint32_t)i * SZ2 : hi2 + (uint32_t)(i - n2_lo) * SZ2; };
+    auto b_slot = [&](int i) -> uint32_t { return B_FIRST ? slot1(i) : slot2(i); };       // activation tile i
+    auto idx_slot = [&](int i) -> uint32_t { return B_FIRST ? slot2(i) : slot1(i); };     // index box i
+    // barriers live in the unused upper halves of the table's first rows
+    uint64_t* b_full = reinterpret_cast<uint64_t*>(lut + 128);       // [NB] activation tile landed
+    uint64_t* a_full = b_full + 6;                                   // [NB] A columns of the stage written
+    uint64_t* st_free = reinterpret_cast<uint64_t*>(lut + 256 + 128);// [NB] MMAs of the stage retired
+    uint64_t* acc_full = st_free + 6;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(st_free + 7);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint64_t* idx_full = reinterpret_cast<uint64_t*>(lut + 512 + 128);   // [NI] index box landed (every copying thread reports)
+    uint64_t* idx_free = idx_full + 8;                                   // [NI] codes read by all dequantising warps
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -144,17 +173,112 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
     const int KS0 = blockIdx.z * a.k_per_split;
     const int NK = (a.k_steps - KS0 < a.k_per_split) ? a.k_steps - KS0 : a.k_per_split;
 
+    // ---- the dequantising threads (warps 2..17; the definitions below are only used by them)
+    const int dw = warp - 2;
+    const int dt = threadIdx.x - 64;              // 0 .. 511
+    const int quarter = warp & 3;                 // TMEM lanes this warp may touch: [32 * quarter, +32)
+    const int kq = dw >> 2;                       // which 32 columns of each stage (warps 2..17: every quarter gets kq = 0..3 once)
+    const int r = 32 * quarter + lane;            // row inside the CTA tile == TMEM lane
+    const int row = o0 + r;
+    const bool row_ok = row < a.out_features;
+    const bool affine = a.group_size > 0;
+
+    // ---- scale / offset of (row, this thread's 32 columns of stage ks)
+    // Staged case (one group per stage, fp32 tables with 16-byte aligned rows - every Qwen2.5 shape):
+    // the 128 rows' values for FOUR stages at a time ride with the index copies as one 16-byte
+    // asynchronous copy per row and table into the unused halves of the codebook table's rows
+    // (two buffers), and a thread picks its row's four values up with one 16-byte shared load.
+    // A per-thread global load instead costs 32 cache-line look-ups per warp instruction, twice per
+    // stage, on the same load/store pipe as the table lookups: it doubled the stage time.
+    // Other layouts (fp16 tables, odd group sizes, shards starting mid-row-of-four) load per thread.
+    // (a K slice must start on a block of four stages: with two buffers, the third block's copy would
+    // otherwise be issued in the prologue, before the first block has been read)
+    const bool st_staged = affine && a.group_size == KS && a.col0 % KS == 0 && a.st_dtype == HXQ_F32 &&
+                           a.ld_st % 4 == 0 && (KS0 & 3) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(a.scales) | reinterpret_cast<uintptr_t>(a.offsets)) & 15) == 0;
+    const int g_base = affine ? a.col0 / a.group_size : 0;
+    // hole h (16 bytes) of buffer b: entries [b][table][row], eight per table row, from table row 8 on
+    auto st_hole = [&](int b, int which, int rr) -> uint32_t {
+        const int h = b * 256 + which * 128 + rr;
+        return lut_base + (uint32_t)((8 + (h >> 3)) * 256 + 128 + (h & 7) * 16);
+    };
+    const int sf_row = dt & 127, sf_which = (dt >> 7) & 1;       // fetch mapping (threads 0..255)
+    const bool sf_ok = st_staged && dt < 256 && o0 + sf_row < a.out_features;
+    const float* sf_src = reinterpret_cast<const float*>(sf_which ? a.offsets : a.scales) +
+                          (int64_t)(sf_ok ? o0 + sf_row : 0) * a.ld_st;
+    auto fetch_st4 = [&](int kj) {     // groups 4 B .. 4 B + 3 of the block B that stage kj belongs to
+        if (st_staged && dt < 256) {
+            const int blk = (KS0 + kj) >> 2;
+            int n = a.n_groups - 4 * blk;
+            n = n > 4 ? 4 : (n < 0 ? 0 : n);
+            const uint32_t bytes = sf_ok ? (uint32_t)(4 * n) : 0u;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;"
+                         :: "r"(st_hole(blk & 1, sf_which, sf_row)), "l"(bytes ? sf_src + 4 * blk : reinterpret_cast<const float*>(a.scales)), "r"(bytes) : "memory");
+        }
+    };
+    auto load_st = [&](int ks, float& s, float& t) {     // the per-thread path
+        s = 1.f; t = 0.f;
+        if (affine && row_ok) {
+            int g = (a.col0 + (KS0 + ks) * KS + kq * 32) / a.group_size - g_base;
+            g = g < a.n_groups ? g : a.n_groups - 1;      // K tail: those activations are zero
+            const int64_t o = (int64_t)row * a.ld_st + g;
+            if (a.st_dtype == HXQ_F32) {
+                s = reinterpret_cast<const float*>(a.scales)[o];
+                t = reinterpret_cast<const float*>(a.offsets)[o];
+            } else {
+                s = __half2float(reinterpret_cast<const __half*>(a.scales)[o]);
+                t = __half2float(reinterpret_cast<const __half*>(a.offsets)[o]);
+            }
+        }
+    };
+
+    // ---- index copies.  Copy mapping (not the row this thread dequantises): chunk q = dt + 512 c,
+    // c = 0, 1: box row q / 8, 16-byte piece q % 8 -> eight consecutive lanes fetch one 128-byte line.
+    const int c_row = dt >> 3, c_piece = dt & 7;                 // second copy: row + 64, same piece
+    const bool c_ok0 = o0 + c_row < a.out_features, c_ok1 = o0 + c_row + 64 < a.out_features;
+    const uint8_t* c_src0 = a.idx + (int64_t)(c_ok0 ? o0 + c_row : 0) * a.ld_idx + (int64_t)KS0 * KS + c_piece * 16;
+    const uint8_t* c_src1 = a.idx + (int64_t)(c_ok1 ? o0 + c_row + 64 : 0) * a.ld_idx + (int64_t)KS0 * KS + c_piece * 16;
+    const uint32_t c_dst0 = (uint32_t)(c_row * 128) + ((uint32_t)(c_piece ^ (c_row & 7)) << 4);
+    const uint32_t c_dst1 = c_dst0 + 64u * 128u;                 // (row + 64) & 7 == row & 7
+    // stages whose 128 columns lie inside the matrix; the copies of later ones are cut at the edge
+    const int full_stages = a.in_features / KS - KS0;
+    auto copy_stage = [&](int kj) {     // this thread's two pieces of stage kj into ring slot kj % NI
+        if (kj < NK) {
+            if (kj == 0 || ((KS0 + kj) & 3) == 0) fetch_st4(kj);
+            const uint32_t box = idx_slot(kj % NI);
+            const bool in_k = kj < full_stages || (int64_t)(KS0 + kj) * KS + c_piece * 16 + 16 <= a.in_features;
+            // rows past the matrix and columns past its end are filled with zeros (source size 0)
+            const uint32_t n0 = (c_ok0 && in_k) ? 16u : 0u, n1 = (c_ok1 && in_k) ? 16u : 0u;
+            const int64_t off = (int64_t)kj * KS;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(box + c_dst0), "l"(n0 ? c_src0 + off : a.idx), "r"(n0) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(box + c_dst1), "l"(n1 ? c_src1 + off : a.idx), "r"(n1) : "memory");
+            // one of the box barrier's 512 expected arrivals, made when this thread's copies so far have landed
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(sm100::smem_u32(&idx_full[kj % NI])) : "memory");
+        }
+    };
+
     if (threadIdx.x == 0) {
-        for (int s = 0; s < MAX_STAGES; ++s) {
-            sm100::mbar_init(&tma_full[s], 1);
+        for (int s = 0; s < NB; ++s) {
+            sm100::mbar_init(&b_full[s], 1);
             sm100::mbar_init(&a_full[s], DEQ_WARPS);
-            sm100::mbar_init(&empty[s], 1);
+            sm100::mbar_init(&st_free[s], 1);
+        }
+        for (int s = 0; s < NI; ++s) {
+            sm100::mbar_init(&idx_full[s], DEQ_THREADS);
+            sm100::mbar_init(&idx_free[s], DEQ_WARPS);
         }
         sm100::mbar_init(acc_full, 1);
         *abort_flag = 0;
         sm100::fence_barrier_init();
-        sm100::prefetch_tensormap(&map_idx);
         sm100::prefetch_tensormap(&map_x);
+    }
+    __syncthreads();          // barriers initialised
+    // The first index boxes are asked for before the rest is set up: the table build and the
+    // tensor-memory allocation below overlap their flight (they touch neither the ring slots nor the
+    // table's holes the scale/offset values go to).
+    if (layout_ok && warp >= 2) {
+#pragma unroll
+        for (int kj = 0; kj < PD; ++kj) copy_stage(kj);
     }
     if (warp == 1) {
         sm100::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -167,28 +291,27 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
     __syncthreads();
     sm100::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a0 = tmem_base + (uint32_t)(BN < 32 ? 32 : BN);   // A stages follow the accumulator's columns
+    const uint32_t tmem_a0 = tmem_base + (uint32_t)(BN < 32 ? 32 : BN);   // the A ring follows the accumulator's columns
 
-    if (STAGES < 2) {   // cannot happen with the sizes above; never run a pipeline that cannot make progress
+    if (!layout_ok) {
         if (threadIdx.x == 0 && a.status != nullptr) atomicExch(a.status, HXQ_E_SHAPE);
     } else if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ activation producer (TMA)
         if (lane == 0) {
             int armed = 0;
             for (int ks = 0; ks < NK; ++ks) {
-                const int s = ks % STAGES;
-                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-                if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-                char* st = stage_ptr(s);
-                sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)STAGE_BYTES);
-                sm100::tma_load_2d(st, &map_idx, &tma_full[s], (KS0 + ks) * KS, o0);
-                sm100::tma_load_2d(st + IDX_BYTES, &map_x, &tma_full[s], (KS0 + ks) * KS, m0);
-                sm100::tma_load_2d(st + IDX_BYTES + BN * 128, &map_x, &tma_full[s], (KS0 + ks) * KS + 64, m0);
+                const int s = ks % NB;
+                const uint32_t ph = (uint32_t)(ks / NB) & 1u;
+                if (!sm100::mbar_wait(&st_free[s], ph ^ 1u, abort_flag)) break;
+                char* bt = smem_raw + (b_slot(s) - smem_base);
+                sm100::mbar_arrive_expect_tx(&b_full[s], (uint32_t)B_BYTES);
+                sm100::tma_load_2d(bt, &map_x, &b_full[s], (KS0 + ks) * KS, m0);
+                sm100::tma_load_2d(bt + BN * 128, &map_x, &b_full[s], (KS0 + ks) * KS + 64, m0);
                 armed = ks + 1;
             }
             if (*abort_flag != 0) {
-                for (int ks = (armed > STAGES ? armed - STAGES : 0); ks < armed; ++ks)
-                    sm100::mbar_wait(&tma_full[ks % STAGES], (uint32_t)(ks / STAGES) & 1u, abort_flag, 200000000LL);
+                for (int ks = (armed > NB ? armed - NB : 0); ks < armed; ++ks)
+                    sm100::mbar_wait(&b_full[ks % NB], (uint32_t)(ks / NB) & 1u, abort_flag, 200000000LL);
             }
         }
     } else if (warp == 1) {
@@ -197,51 +320,28 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
             constexpr uint32_t idesc = sm100::make_idesc_bf16(BM, BN);
             bool ok = true;
             for (int ks = 0; ks < NK && ok; ++ks) {
-                const int s = ks % STAGES;
-                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-                ok = sm100::mbar_wait(&tma_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
+                const int s = ks % NB;
+                const uint32_t ph = (uint32_t)(ks / NB) & 1u;
+                ok = sm100::mbar_wait(&b_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
                 if (!ok) break;
                 sm100::tc_fence_after_sync();
-                char* st = stage_ptr(s);
+                // B: sub-tile kk / 4 (64 K columns each), + 32 bytes (2 in descriptor units) per 16-column slice
+                const uint64_t db0 = sm100::make_desc_k_sw128(b_slot(s));
+                const uint32_t ta = tmem_a0 + (uint32_t)(s * A_COLS);
 #pragma unroll
                 for (int kk = 0; kk < KS / 16; ++kk) {
-                    // B: sub-tile kk / 4 (64 K columns each), + 32 bytes per 16-column slice inside it
-                    const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(st + IDX_BYTES + (kk >> 2) * (BN * 128))) +
-                                        (uint64_t)(2 * (kk & 3));
-                    umma_bf16_ts(tmem_base, tmem_a0 + (uint32_t)(s * A_COLS + kk * 8), db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                    const uint64_t db = db0 + (uint64_t)((kk >> 2) * (BN * 128 / 16) + 2 * (kk & 3));
+                    umma_bf16_ts(tmem_base, ta + (uint32_t)(kk * 8), db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
                 }
-                sm100::umma_commit(&empty[s]);
+                sm100::umma_commit(&st_free[s]);
             }
             if (ok) sm100::umma_commit(acc_full);
         }
     } else {
         // ------------------------------------------------------------ dequantising warps
-        const int dw = warp - 2;
-        const int quarter = warp & 3;                 // TMEM lanes this warp may touch: [32 * quarter, +32)
-        const int kq = dw >> 2;                       // which 32 columns of each stage (warps 2..17: every quarter gets kq = 0..3 once)
-        const int r = 32 * quarter + lane;            // row inside the CTA tile == TMEM lane
-        const int row = o0 + r;
-        const bool row_ok = row < a.out_features;
         const uint32_t lane_key = lut_base | ((uint32_t)lane << 2);
-        const bool affine = a.group_size > 0;
-        const int g_base = affine ? a.col0 / a.group_size : 0;
         const uint32_t t_row = tmem_a0 + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(kq * 16);
 
-        auto load_st = [&](int ks, float& s, float& t) {
-            s = 1.f; t = 0.f;
-            if (affine && row_ok) {
-                int g = (a.col0 + (KS0 + ks) * KS + kq * 32) / a.group_size - g_base;
-                g = g < a.n_groups ? g : a.n_groups - 1;      // K tail: those activations are zero
-                const int64_t o = (int64_t)row * a.ld_st + g;
-                if (a.st_dtype == HXQ_F32) {
-                    s = reinterpret_cast<const float*>(a.scales)[o];
-                    t = reinterpret_cast<const float*>(a.offsets)[o];
-                } else {
-                    s = __half2float(reinterpret_cast<const __half*>(a.scales)[o]);
-                    t = __half2float(reinterpret_cast<const __half*>(a.offsets)[o]);
-                }
-            }
-        };
         // sidecar cursor of this row: entries are sorted by column; this thread takes those inside its
         // 32 columns of every stage and steps over the others
         // (two entries are held ahead: the loads that refill them are not waited for inside the stage)
@@ -255,45 +355,68 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
             if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
             if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; }
         }
-        float sc_n, of_n;
-        load_st(0, sc_n, of_n);
-        if (kq == 0 && row_ok) {
-            for (int pk = 0; pk < kPrefetch && pk < NK; ++pk) {
-                const int64_t col = (int64_t)(KS0 + pk) * KS;
-                if (col < a.in_features) asm volatile("prefetch.global.L2 [%0];" :: "l"(a.idx + (int64_t)row * a.ld_idx + col));
-            }
-        }
-        int done = 0;
+        float sc_n = 1.f, of_n = 0.f;
+        if (!st_staged) load_st(0, sc_n, of_n);
+        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        bool failed = false;          // one of this thread's bounded waits gave up (or saw the abort flag)
+        int stored = -1;              // last stage whose tcgen05.st was issued and not yet handed over
+        auto hand_over = [&]() {      // the pending store has completed: let the MMA warp have the stage
+            tmem_st_wait();
+            sm100::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) sm100::mbar_arrive(&a_full[stored % NB]);
+            stored = -1;
+        };
         for (int ks = 0; ks < NK; ++ks) {
-            const int s = ks % STAGES;
-            const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-            const float sc = sc_n, of = of_n;
-            if (ks + 1 < NK) load_st(ks + 1, sc_n, of_n);
-            // A stage's index box is one 128-byte line of each of 128 rows, and an SM's bulk-copy unit
-            // keeps too few such lines in flight to cover DRAM latency.  So the row's line of a stage
-            // kPrefetch ahead is asked into L2 now (one thread per row and stage; nothing comes back).
-            if (kq == 0 && row_ok && ks + kPrefetch < NK) {
-                const int64_t col = (int64_t)(KS0 + ks + kPrefetch) * KS;
-                if (col < a.in_features)
-                    asm volatile("prefetch.global.L2 [%0];" :: "l"(a.idx + (int64_t)row * a.ld_idx + col));
+            if (ks + PD < NK) {
+                // the box of stage ks + PD held stage ks - 1: wait until every warp has its codes in registers
+                if (ks >= 1 && !__all_sync(0xffffffffu, sm100::mbar_wait(&idx_free[(ks + PD) % NI], (uint32_t)((ks + PD) / NI - 1) & 1u, abort_flag))) {
+                    failed = true;
+                    break;
+                }
+                copy_stage(ks + PD);
             }
-            if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
-            const uint32_t idx_row = sm100::smem_u32(stage_ptr(s)) + (uint32_t)(r * 128);
+            if (!__all_sync(0xffffffffu, sm100::mbar_wait(&idx_full[ks % NI], (uint32_t)(ks / NI) & 1u, abort_flag))) {
+                failed = true;
+                break;
+            }
+            float sc, of;
+            if (st_staged) {
+                const int ak = KS0 + ks;
+                if (ks == 0 || (ak & 3) == 0) {
+                    const uint32_t hs = st_hole((ak >> 2) & 1, 0, r), ht = st_hole((ak >> 2) & 1, 1, r);
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(s4.x), "=f"(s4.y), "=f"(s4.z), "=f"(s4.w) : "r"(hs));
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t4.x), "=f"(t4.y), "=f"(t4.z), "=f"(t4.w) : "r"(ht));
+                }
+                const int q = ak & 3;
+                sc = q == 0 ? s4.x : (q == 1 ? s4.y : (q == 2 ? s4.z : s4.w));
+                of = q == 0 ? t4.x : (q == 1 ? t4.y : (q == 2 ? t4.z : t4.w));
+            } else {
+                sc = sc_n; of = of_n;
+                if (ks + 1 < NK) load_st(ks + 1, sc_n, of_n);
+            }
+            uint32_t w[8];
+            {
+                const uint32_t idx_row = idx_slot(ks % NI) + (uint32_t)(r * 128);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {     // 16 codes per load: chunk 2 * kq + c of the row, swizzled by the row
+                    const uint32_t addr = idx_row + ((uint32_t)((2 * kq + c) ^ (r & 7)) << 4);
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3]) : "r"(addr));
+                }
+            }
+            // the codes are (on their way) in registers: the box can be refilled
+            __syncwarp();
+            if (lane == 0) sm100::mbar_arrive(&idx_free[ks % NI]);
             uint32_t out[16];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {     // 16 codes per load: chunk 2 * kq + c of the row, swizzled by the row
-                const uint32_t addr = idx_row + ((uint32_t)((2 * kq + c) ^ (r & 7)) << 4);
-                uint32_t w[4];
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
-#pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    const uint32_t a0 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)((j & 3) << 4));
-                    const uint32_t a1 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)(((j + 1) & 3) << 4));
-                    float v0, v1;
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v0) : "r"(a0));
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v1) : "r"(a1));
-                    out[c * 8 + (j >> 1)] = pack_bf16x2(fmaf(v0, sc, of), fmaf(v1, sc, of));
-                }
+            for (int j = 0; j < 32; j += 2) {
+                const uint32_t a0 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)((j & 3) << 4));
+                const uint32_t a1 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)(((j + 1) & 3) << 4));
+                float v0, v1;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v0) : "r"(a0));
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v1) : "r"(a1));
+                out[j >> 1] = pack_bf16x2(fmaf(v0, sc, of), fmaf(v1, sc, of));
             }
             // sidecar entries of this row inside this stage: mine are patched into the packed registers
             // (a jump per entry instead of a dynamically indexed register array), the others skipped
@@ -329,30 +452,28 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
                 }
             }
             __syncwarp();
-            // the previous stage's store has had this stage's lookups to complete: hand that stage over
-            // now, then start this stage's store
-            if (ks > 0) {
-                tmem_st_wait();
-                sm100::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) sm100::mbar_arrive(&a_full[(ks - 1) % STAGES]);
+            // the previous stage's store has had these lookups to complete
+            if (stored >= 0) hand_over();
+            // the A columns of this ring slot are free once the MMAs that read them NB stages ago have retired
+            const int sb = ks % NB;
+            // (warp-uniform outcome: the store below is a whole-warp instruction)
+            if (ks >= NB && !__all_sync(0xffffffffu, sm100::mbar_wait(&st_free[sb], (uint32_t)(ks / NB - 1) & 1u, abort_flag))) {
+                failed = true;
+                break;
             }
-            tmem_st_32x16(t_row + (uint32_t)(s * A_COLS), out);
-            done = ks + 1;
+            sm100::tc_fence_after_sync();
+            tmem_st_32x16(t_row + (uint32_t)(sb * A_COLS), out);
+            stored = ks;
         }
-        if (done > 0) {   // the last stage stored (a wait that gave up leaves `done` at the last stored stage)
-            tmem_st_wait();
-            sm100::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) sm100::mbar_arrive(&a_full[(done - 1) % STAGES]);
-        }
+        if (stored >= 0) hand_over();
+        asm volatile("cp.async.wait_all;" ::: "memory");   // (a loop left early must not retire with copies in flight)
 
         // ------------------------------------------------------------ epilogue
         // the four warps of a quarter split the token columns
         {
             constexpr int COLS_PER_WARP = BN / 4 < 8 ? 8 : BN / 4;   // 8, 16 or 32 (16 tokens: two of the four warps)
             const int c_lo = kq * COLS_PER_WARP;
-            if (c_lo < BN && sm100::mbar_wait(acc_full, 0u, abort_flag)) {
+            if (!failed && c_lo < BN && sm100::mbar_wait(acc_full, 0u, abort_flag)) {
                 sm100::tc_fence_after_sync();
                 float* part = a.partial ? a.partial + (int64_t)blockIdx.z * a.M * a.out_features : nullptr;
                 const float bias = (a.bias != nullptr && row_ok && part == nullptr) ? a.bias[row] : 0.f;
@@ -386,8 +507,14 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constan
         sm100::tc_fence_after_sync();
         sm100::tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (threadIdx.x == 0 && *abort_flag != 0 && a.status != nullptr) atomicExch(a.status, HXQ_E_TIMEOUT);
+    if (threadIdx.x == 0 && *abort_flag == 1 && a.status != nullptr) atomicExch(a.status, HXQ_E_TIMEOUT);
 }
+
+}  // namespace gemmts
+}  // namespace hxq
+
+namespace hxq {
+namespace gemmts {
 
 // ---- host side ---------------------------------------------------------------------
 
@@ -435,8 +562,7 @@ size_t split_bytes(const hxq_desc* d, int32_t M) {
 }
 
 template <int BN>
-static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, int grid_m, int grid_o, int splits,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& mx, const Args& a, int grid_m, int grid_o, int splits, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -445,7 +571,7 @@ static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, i
             return HXQ_E_DEVICE;
         attr_set[dev] = true;
     }
-    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mi, mx, a);
+    gemm_ts_kernel<BN><<<dim3(grid_m, grid_o, splits), NUM_THREADS, SMEM_TOTAL, stream>>>(mx, a);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
 }
 
@@ -454,10 +580,7 @@ static int launch(const CUtensorMap& mi, const CUtensorMap& mx, const Args& a, i
 int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, void* y, int y_dtype, int64_t ldy,
         void* split_ws, size_t split_ws_bytes, int32_t* status_word, cudaStream_t stream) {
     const int BN = pick_bn(M);
-    CUtensorMap mi, mx;
-    if (!gemm::make_map_2d(&mi, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->indices, (uint64_t)d->in_features,
-                           (uint64_t)d->out_features, (uint64_t)d->ld_idx, KS, BM, CU_TENSOR_MAP_SWIZZLE_128B))
-        return HXQ_E_DEVICE;
+    CUtensorMap mx;
     if (!gemm::make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, xb, (uint64_t)d->in_features, (uint64_t)M,
                            (uint64_t)ldxb * 2, 64, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return HXQ_E_DEVICE;
@@ -478,17 +601,17 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
     a.partial = nullptr;
     if (splits > 1 && split_ws && aligned_to(split_ws, 16) &&
         split_ws_bytes >= (size_t)splits * M * d->out_features * sizeof(float)) {
-        a.k_per_split = (a.k_steps + splits - 1) / splits;
+        a.k_per_split = ((a.k_steps + splits - 1) / splits + 3) & ~3;   // whole blocks of four stages (scale/offset staging)
         splits = (a.k_steps + a.k_per_split - 1) / a.k_per_split;   // no empty slice
         a.partial = reinterpret_cast<float*>(split_ws);
     } else {
         splits = 1;
     }
     int st;
-    if (BN == 128) st = launch<128>(mi, mx, a, grid_m, grid_o, splits, stream);
-    else if (BN == 64) st = launch<64>(mi, mx, a, grid_m, grid_o, splits, stream);
-    else if (BN == 32) st = launch<32>(mi, mx, a, grid_m, grid_o, splits, stream);
-    else st = launch<16>(mi, mx, a, grid_m, grid_o, splits, stream);
+    if (BN == 128) st = launch<128>(mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 64) st = launch<64>(mx, a, grid_m, grid_o, splits, stream);
+    else if (BN == 32) st = launch<32>(mx, a, grid_m, grid_o, splits, stream);
+    else st = launch<16>(mx, a, grid_m, grid_o, splits, stream);
     if (st != HXQ_OK || splits == 1) return st;
     gemm::launch_splitk_reduce(a.partial, splits, M, d->out_features, d->bias, y, y_dtype, ldy, stream);
     return cudaGetLastError() == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
