@@ -133,7 +133,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
     constexpr int B_BYTES = BN * KS * 2;                 // two [BN x 64] bf16 sub-tiles
     constexpr int NB = Rings<BN>::NB;
     constexpr int NI = Rings<BN>::NI;
-    constexpr int PD = NI - 1;                           // stages the index copies run ahead
+    // stages the index copies run ahead: one box of slack where the ring is deep enough, so that a warp
+    // can start the next stage while the slowest warp is still reading the previous one
+    constexpr int PD = NI >= 5 ? NI - 2 : NI - 1;
     static_assert((BN < 32 ? 32 : BN) + NB * A_COLS <= TMEM_COLS, "accumulator + A ring must fit tensor memory");
     static_assert(NI >= 2 && NI <= 8 && NB >= 2 && NB <= 6, "barrier and slot-table layout");
     extern __shared__ __align__(1024) char smem_raw[];
@@ -272,11 +274,34 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
         sm100::fence_barrier_init();
         sm100::prefetch_tensormap(&map_x);
     }
+    // ---- sidecar of this row tile: the CSR entries of rows o0 .. o0 + 127 are one contiguous run of
+    // cols[] / deltas[]; up to SC_MAX of them are copied into the table's unused halves (rows 72 ..),
+    // so that the per-thread cursors below read shared memory.  (Cursors on global memory made every
+    // warp wait, once per stage, for the DRAM miss of the previous stage's cursor refill: that wait,
+    // not the lookups, set the stage time.)  A tile with more entries keeps its cursors on global memory.
+    constexpr int SC_MAX = 2944, SC_ROW_C = 72, SC_ROW_D = SC_ROW_C + SC_MAX / 32;   // (0.1 % of 128 x 18944 weights is 2425)
+    static_assert(SC_ROW_D + SC_MAX / 32 <= 256, "sidecar staging must fit the table's rows");
+    int sc_e0 = 0, sc_n = 0;
+    if (a.rowptr != nullptr) {
+        const int o1 = o0 + BM < a.out_features ? o0 + BM : a.out_features;
+        sc_e0 = a.rowptr[o0];
+        sc_n = a.rowptr[o1] - sc_e0;
+    }
+    const bool sc_staged = sc_n <= SC_MAX;
+    auto sc_addr = [&](int base_row, int e) -> uint32_t {     // entry e (relative to the tile's first)
+        return lut_base + ((uint32_t)(base_row + (e >> 5)) << 8) + 128u + ((uint32_t)(e & 31) << 2);
+    };
     __syncthreads();          // barriers initialised
     // The first index boxes are asked for before the rest is set up: the table build and the
     // tensor-memory allocation below overlap their flight (they touch neither the ring slots nor the
     // table's holes the scale/offset values go to).
     if (layout_ok && warp >= 2) {
+        if (sc_staged) {     // (these copies are covered by the first box's barrier arrival below)
+            for (int e = dt; e < sc_n; e += DEQ_THREADS) {
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(sc_addr(SC_ROW_C, e)), "l"(a.cols + sc_e0 + e) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(sc_addr(SC_ROW_D, e)), "l"(a.deltas + sc_e0 + e) : "memory");
+            }
+        }
 #pragma unroll
         for (int kj = 0; kj < PD; ++kj) copy_stage(kj);
     }
@@ -302,7 +327,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
             for (int ks = 0; ks < NK; ++ks) {
                 const int s = ks % NB;
                 const uint32_t ph = (uint32_t)(ks / NB) & 1u;
-                if (!sm100::mbar_wait(&st_free[s], ph ^ 1u, abort_flag)) break;
+                if (!sm100::mbar_wait(&st_free[s], ph ^ 1u, abort_flag, 2000000000LL, 200u)) break;
                 char* bt = smem_raw + (b_slot(s) - smem_base);
                 sm100::mbar_arrive_expect_tx(&b_full[s], (uint32_t)B_BYTES);
                 sm100::tma_load_2d(bt, &map_x, &b_full[s], (KS0 + ks) * KS, m0);
@@ -322,7 +347,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
             for (int ks = 0; ks < NK && ok; ++ks) {
                 const int s = ks % NB;
                 const uint32_t ph = (uint32_t)(ks / NB) & 1u;
-                ok = sm100::mbar_wait(&b_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
+                ok = sm100::mbar_wait(&b_full[s], ph, abort_flag, 2000000000LL, 50u) && sm100::mbar_wait(&a_full[s], ph, abort_flag, 2000000000LL, 50u);
                 if (!ok) break;
                 sm100::tc_fence_after_sync();
                 // B: sub-tile kk / 4 (64 K columns each), + 32 bytes (2 in descriptor units) per 16-column slice
@@ -343,20 +368,31 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
         const uint32_t t_row = tmem_a0 + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(kq * 16);
 
         // sidecar cursor of this row: entries are sorted by column; this thread takes those inside its
-        // 32 columns of every stage and steps over the others
-        // (two entries are held ahead: the loads that refill them are not waited for inside the stage)
-        int e_cur = 0, e_end = 0, nc = 0x7fffffff, nc1 = 0x7fffffff;
-        float nd = 0.f, nd1 = 0.f;
+        // 32 columns of every stage and steps over the others.  e_cur / e_end count from the tile's first
+        // entry; nc is the column of entry e_cur (read when the cursor moves).
+        int e_cur = 0, e_end = 0, nc = 0x7fffffff;
         if (a.rowptr != nullptr && row_ok) {
-            e_cur = a.rowptr[row];
-            e_end = a.rowptr[row + 1];
-            const int k_first = KS0 * KS;
-            while (e_cur < e_end && a.cols[e_cur] < k_first) ++e_cur;
-            if (e_cur < e_end) { nc = a.cols[e_cur]; nd = a.deltas[e_cur]; }
-            if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; }
+            e_cur = a.rowptr[row] - sc_e0;
+            e_end = a.rowptr[row + 1] - sc_e0;
         }
-        float sc_n = 1.f, of_n = 0.f;
-        if (!st_staged) load_st(0, sc_n, of_n);
+        auto sc_col = [&](int e) -> int {
+            if (sc_staged) {
+                int v;
+                asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(sc_addr(SC_ROW_C, e)));
+                return v;
+            }
+            return a.cols[sc_e0 + e];
+        };
+        auto sc_delta = [&](int e) -> float {
+            if (sc_staged) {
+                float v;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(sc_addr(SC_ROW_D, e)));
+                return v;
+            }
+            return a.deltas[sc_e0 + e];
+        };
+        float st_s_n = 1.f, st_t_n = 0.f;
+        if (!st_staged) load_st(0, st_s_n, st_t_n);
         float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), t4 = make_float4(0.f, 0.f, 0.f, 0.f);
         bool failed = false;          // one of this thread's bounded waits gave up (or saw the abort flag)
         int stored = -1;              // last stage whose tcgen05.st was issued and not yet handed over
@@ -369,8 +405,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
         };
         for (int ks = 0; ks < NK; ++ks) {
             if (ks + PD < NK) {
-                // the box of stage ks + PD held stage ks - 1: wait until every warp has its codes in registers
-                if (ks >= 1 && !__all_sync(0xffffffffu, sm100::mbar_wait(&idx_free[(ks + PD) % NI], (uint32_t)((ks + PD) / NI - 1) & 1u, abort_flag))) {
+                // the box of stage ks + PD held stage ks + PD - NI: wait until every warp has those codes in registers
+                if (ks + PD >= NI && !__all_sync(0xffffffffu, sm100::mbar_wait(&idx_free[(ks + PD) % NI], (uint32_t)((ks + PD) / NI - 1) & 1u, abort_flag))) {
                     failed = true;
                     break;
                 }
@@ -379,6 +415,11 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
             if (!__all_sync(0xffffffffu, sm100::mbar_wait(&idx_full[ks % NI], (uint32_t)(ks / NI) & 1u, abort_flag))) {
                 failed = true;
                 break;
+            }
+            if (ks == 0) {     // the staged sidecar has landed with the first box: position the cursor
+                const int k_first = KS0 * KS;
+                while (e_cur < e_end && sc_col(e_cur) < k_first) ++e_cur;
+                nc = e_cur < e_end ? sc_col(e_cur) : 0x7fffffff;
             }
             float sc, of;
             if (st_staged) {
@@ -392,8 +433,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                 sc = q == 0 ? s4.x : (q == 1 ? s4.y : (q == 2 ? s4.z : s4.w));
                 of = q == 0 ? t4.x : (q == 1 ? t4.y : (q == 2 ? t4.z : t4.w));
             } else {
-                sc = sc_n; of = of_n;
-                if (ks + 1 < NK) load_st(ks + 1, sc_n, of_n);
+                sc = st_s_n; of = st_t_n;
+                if (ks + 1 < NK) load_st(ks + 1, st_s_n, st_t_n);
             }
             uint32_t w[8];
             {
@@ -427,6 +468,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                     const int j = nc - k_lo;
                     if (j >= 0 && j < 32) {
                         const int hi = j & 1;
+                        const float nd = sc_delta(e_cur);
                         switch (j >> 1) {
                             case 0: out[0] = add_to_half(out[0], hi, nd); break;
                             case 1: out[1] = add_to_half(out[1], hi, nd); break;
@@ -447,8 +489,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                         }
                     }
                     ++e_cur;
-                    nc = nc1; nd = nd1;
-                    if (e_cur + 1 < e_end) { nc1 = a.cols[e_cur + 1]; nd1 = a.deltas[e_cur + 1]; } else { nc1 = 0x7fffffff; }
+                    nc = e_cur < e_end ? sc_col(e_cur) : 0x7fffffff;
                 }
             }
             __syncwarp();

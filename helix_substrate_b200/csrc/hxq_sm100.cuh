@@ -57,13 +57,19 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
 // of the CTA has given up (*abort != 0); on giving up it raises *abort itself.
 // Returns false when the wait did not complete.  While the phase is pending the thread sleeps in
 // the barrier unit (a few microseconds per try), so waiting warps leave the issue slots to the
-// warps that work.
+// warps that work; the abort flag and the clock are looked at once per 32 tries only (a poll is
+// then a try, a count and a branch).  `nap_ns` > 0 adds a sleep of that length after every failed
+// try: for single-lane roles whose reaction time does not matter.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
-                                          long long limit = 2000000000LL) {
+                                          long long limit = 2000000000LL, uint32_t nap_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
+            if (nap_ns) __nanosleep(nap_ns);
+        }
         if (*abort != 0) return false;
         if (clock64() - t0 > limit) {
             *abort = 1;

@@ -297,14 +297,16 @@ def test_gemm_vs_oracle(shape, M):
     assert torch.equal(y, w.matmul(x, out_dtype=torch.float32, force="gemm"))
 
 
-def test_gemm_sidecar_is_applied():
+@pytest.mark.parametrize("nnz,M", [(2000, 64), (2000, 600), (9000, 24), (9000, 100)])
+def test_gemm_sidecar_is_applied(nnz, M):
     """With a zero codebook the product is the sidecar alone: every entry must
-    land in the right (row, column) of the dequantised tile."""
+    land in the right (row, column) of the dequantised tile.  9000 entries over 256 rows are more
+    per 128-row tile than the small-token kernel keeps in shared memory (its cursors then stay on
+    global memory)."""
     rng = np.random.default_rng(2)
-    n_out, n_in, M = 256, 1024, 64
+    n_out, n_in = 256, 1024
     cb = np.zeros(256, np.float32)
     idx = rng.integers(0, 256, (n_out, n_in), dtype=np.uint8)
-    nnz = 2000
     pos = np.sort(rng.choice(n_out * n_in, nnz, replace=False)).astype(np.int64)
     vals = rng.standard_normal(nnz).astype(np.float16).astype(np.float32)
     dense = np.zeros(n_out * n_in, np.float32)
