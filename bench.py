@@ -315,9 +315,13 @@ def block_gemv_m(layers, M: int, dev, min_s: float) -> dict:
     nbytes = algorithmic_bytes(layers, M, 2)
     peak, kind = _hbm_peak()
     gbs = nbytes / (ms * 1e-3) / 1e9
-    launches = 3 * len(layers) * (-(-M // 4))
+    from helix_substrate_b200.packed import uses_gemv
+    if uses_gemv(M, act):      # fp32-accumulate decode kernel: four tokens per launch
+        kernel, launches = "hxq_gemv (gemv_lean_kernel)", 3 * len(layers) * (-(-M // 4))
+    else:                         # tensor-memory kernel: one launch per linear, + the split-K sum where the row-tile grid is small (down)
+        kernel, launches = "hxq_gemm (gemm_ts_kernel)", 4 * len(layers)
     return {"m": M, "GBps": gbs, "ms_per_step": ms, "steps": n, "us_per_linear": ms * 1e3 / (3 * len(layers)),
-            "launches_per_step": launches, "frac_of_hbm_peak": gbs / peak, "peak_kind": f"of {kind}", "clocks": clk}
+            "kernel": kernel, "launches_per_step": launches, "frac_of_hbm_peak": gbs / peak, "peak_kind": f"of {kind}", "clocks": clk}
 
 
 def block_prefill(Ms, dev, min_s: float) -> dict:
