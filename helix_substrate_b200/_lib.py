@@ -96,6 +96,9 @@ def lib() -> C.CDLL:
     L.hxq_attn_decode.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                   C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_float, C.c_void_p]
+    L.hxq_dense_gemv.restype = C.c_int
+    L.hxq_dense_gemv.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
+                                 C.c_int, C.c_int64, C.c_void_p]
     L.hxq_swiglu.restype = C.c_int
     L.hxq_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                              C.c_int64, C.c_void_p]

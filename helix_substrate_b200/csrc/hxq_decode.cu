@@ -406,6 +406,105 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv
     }
 }
 
+
+// ---- dense bf16 weight x up to four tokens (the decoder's lm_head at decode time) -------------------
+// y[m, o] = sum_i x[m, i] * W[o, i].  HBM-bound on W (2 bytes per weight, each read once): a warp
+// owns FOUR rows at a time, a lane 16 bytes (8 weights) of every 512-byte piece of each, two pieces
+// of the four rows (eight loads) in flight per lane; the activations sit in shared memory as fp32 and
+// a lane's eight values per token are read once per piece for all four rows (one row per read made
+// the shared-memory pipe, not HBM, the limit from two tokens on); fp32 accumulation, one warp
+// reduction per row.  W is long-lived (see the weight precondition of the compressed products): its
+// first loads are issued before the wait for the previous kernel.
+template <int MP>
+__global__ void __launch_bounds__(256) dense_gemv_kernel(const __nv_bfloat16* __restrict__ W, int64_t ldw, int n_out, int n_in,
+                                                         const __nv_bfloat16* __restrict__ x, int64_t ldx, void* y, int y_dtype,
+                                                         int64_t ldy, int M) {
+    extern __shared__ __align__(16) float xs[];          // [MP][n_in]
+    constexpr int R = 4, U = 2;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int n_chunk = n_in >> 3;
+    const int groups_total = gridDim.x * (blockDim.x >> 5);
+    const int n_groups = (n_out + R - 1) / R;
+    int grp = blockIdx.x * (blockDim.x >> 5) + warp;
+    uint4 w[R][U];
+    auto load_w = [&](int g, int c0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int row = g * R + r;
+            const uint4* p = reinterpret_cast<const uint4*>(W + (int64_t)(row < n_out ? row : 0) * ldw);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = c0 + u * 32 + lane;
+                w[r][u] = (c < n_chunk && row < n_out) ? __ldcs(p + c) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (grp < n_groups) load_w(grp, 0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = threadIdx.x; i < MP * n_in; i += blockDim.x) {
+        const int m = i / n_in, k = i - m * n_in;
+        xs[i] = m < M ? __bfloat162float(x[(int64_t)m * ldx + k]) : 0.f;
+    }
+    __syncthreads();
+    for (; grp < n_groups; grp += groups_total) {
+        float acc[R][MP];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MP; ++m) acc[r][m] = 0.f;
+        for (int c0 = 0; c0 < n_chunk; c0 += U * 32) {
+            if (c0 > 0) load_w(grp, c0);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = c0 + u * 32 + lane;
+                if (c < n_chunk) {
+                    float xf[MP][8];
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(xs + m * n_in + c * 8);
+                        const float4 x1 = *reinterpret_cast<const float4*>(xs + m * n_in + c * 8 + 4);
+                        xf[m][0] = x0.x; xf[m][1] = x0.y; xf[m][2] = x0.z; xf[m][3] = x0.w;
+                        xf[m][4] = x1.x; xf[m][5] = x1.y; xf[m][6] = x1.z; xf[m][7] = x1.w;
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t q[4] = {w[r][u].x, w[r][u].y, w[r][u].z, w[r][u].w};
+                        float wf[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            wf[2 * j] = __uint_as_float(q[j] << 16);
+                            wf[2 * j + 1] = __uint_as_float(q[j] & 0xffff0000u);
+                        }
+#pragma unroll
+                        for (int m = 0; m < MP; ++m) {
+                            float a = acc[r][m];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) a = fmaf(wf[j], xf[m][j], a);
+                            acc[r][m] = a;
+                        }
+                    }
+                }
+            }
+        }
+        // the next rows' first pieces are on their way while these rows are reduced and stored
+        const int next = grp + groups_total;
+        if (next < n_groups) load_w(next, 0);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int row = grp * R + r;
+#pragma unroll
+            for (int m = 0; m < MP; ++m) {
+                float v = acc[r][m];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (lane == 0 && m < M && row < n_out) store_from_f32(y, (int64_t)m * ldy + row, v, y_dtype);
+            }
+        }
+    }
+}
+
 }  // namespace dec
 }  // namespace hxq
 
@@ -473,4 +572,41 @@ extern "C" int hxq_swiglu(const void* gate, const void* up, void* out, int32_t B
         reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(gate),
         reinterpret_cast<const __nv_bfloat16*>(up), reinterpret_cast<__nv_bfloat16*>(out), (int)n, ld_gate, ld_up, ld_out);
     return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+template <int MP>
+static int launch_dense_gemv(const __nv_bfloat16* W, int64_t ldw, int n_out, int n_in, const __nv_bfloat16* x, int64_t ldx,
+                             void* y, int y_dtype, int64_t ldy, int M, cudaStream_t stream) {
+    const size_t smem = (size_t)MP * n_in * sizeof(float);
+    static size_t smem_set[64] = {0};
+    int dev = 0, n_sm = 148, occ = 1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HXQ_E_DEVICE;
+    if (smem > 48 * 1024 && smem_set[dev] < smem) {
+        if (cudaFuncSetAttribute(dense_gemv_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return HXQ_E_SHAPE;
+        smem_set[dev] = smem;
+    }
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, dense_gemv_kernel<MP>, 256, smem) != cudaSuccess || occ < 1) occ = 1;
+    int grid = n_sm * occ;
+    const int need = (n_out + 31) / 32;      // eight warps of four rows per CTA
+    if (grid > need) grid = need;
+    const cudaError_t e = launch_pdl(dense_gemv_kernel<MP>, dim3(grid), dim3(256), smem, stream, W, ldw, n_out, n_in, x, ldx, y,
+                                     y_dtype, ldy, M);
+    return e == cudaSuccess ? HXQ_OK : HXQ_E_LAUNCH;
+}
+
+extern "C" int hxq_dense_gemv(const void* weight, int32_t out_features, int32_t in_features, int64_t ldw, const void* x,
+                              int32_t M, int64_t ldx, void* y, int y_dtype, int64_t ldy, hxq_stream_t stream_) {
+    if (!weight || !x || !y || out_features <= 0 || in_features <= 0 || M <= 0 || M > 4) return HXQ_E_ARG;
+    if (in_features % 8 != 0 || in_features > 12288 || ldw < in_features || ldw % 8 != 0 || ldx < in_features || ldy < out_features)
+        return HXQ_E_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(weight) & 15) != 0) return HXQ_E_ALIGN;
+    if (y_dtype != HXQ_F32 && y_dtype != HXQ_F16 && y_dtype != HXQ_BF16) return HXQ_E_DTYPE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(weight);
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    if (M == 1) return launch_dense_gemv<1>(W, ldw, out_features, in_features, xb, ldx, y, y_dtype, ldy, M, stream);
+    if (M == 2) return launch_dense_gemv<2>(W, ldw, out_features, in_features, xb, ldx, y, y_dtype, ldy, M, stream);
+    return launch_dense_gemv<4>(W, ldw, out_features, in_features, xb, ldx, y, y_dtype, ldy, M, stream);
 }

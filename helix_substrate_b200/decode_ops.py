@@ -82,3 +82,26 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor) -> torch.Ten
                                    up.stride(0), out.stride(0), _stream(gate.device))
     _lib.check(st, "hxq_swiglu")
     return out
+
+
+DENSE_GEMV_MAX_M = 4      # what the kernel takes
+DENSE_GEMV_USE_M = 2      # where it beats a library GEMM (measured: 158 vs 179 us at one token, 230 vs 180 us at four, [152064, 3584])
+
+
+def dense_gemv(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None,
+               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """y = x @ weight.t() for a dense bf16 weight [OUT, IN] and up to four bf16 tokens (lm_head at
+    decode time; the reference runs it as _BF16Linear, helix_substrate/basin_runtime.py:181-205)."""
+    _bf16_rows(weight, "weight"); _bf16_rows(x, "x")
+    M, n_in = x.shape
+    n_out = weight.shape[0]
+    assert weight.shape[1] == n_in and 0 < M <= DENSE_GEMV_MAX_M
+    if out is None:
+        out = torch.empty(M, n_out, device=x.device, dtype=out_dtype)
+    dt = {torch.float32: _lib.HXQ_F32, torch.float16: _lib.HXQ_F16, torch.bfloat16: _lib.HXQ_BF16}[out.dtype]
+    assert out.shape == (M, n_out) and out.stride(1) == 1
+    with torch.cuda.device(x.device):
+        st = _lib.lib().hxq_dense_gemv(_p(weight), n_out, n_in, weight.stride(0), _p(x), M, x.stride(0), _p(out), dt,
+                                       out.stride(0), _stream(x.device))
+    _lib.check(st, "hxq_dense_gemv")
+    return out

@@ -333,6 +333,8 @@ class Qwen2HxqDecoder(nn.Module):
             delta = yield (*row_parallel(L.down_proj, sb["act"], "d2"), w_next)
             if delta is not None:
                 decode_ops.add_rmsnorm(h, delta, w_next, eps, x)
+        if x.shape[0] <= decode_ops.DENSE_GEMV_USE_M:      # one or two tokens: the streaming kernel; more: a library GEMM
+            return decode_ops.dense_gemv(self.lm_head, x)
         return x @ self.lm_head.t()
 
     @torch.no_grad()

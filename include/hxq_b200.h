@@ -226,6 +226,15 @@ int hxq_attn_decode(const void* q, int64_t ld_q, const void* k_cache, const void
 int hxq_swiglu(const void* gate, const void* up, void* out, int32_t B, int32_t n, int64_t ld_gate,
                int64_t ld_up, int64_t ld_out, hxq_stream_t stream);
 
+/* y[m, o] = sum_i x[m, i] * weight[o, i] for a DENSE bf16 weight [out_features, ldw] and up to four
+ * tokens of bf16 activations: the decoder's lm_head at decode time, which the reference keeps dense
+ * (helix_substrate/tensor_policy.py:199-208) and runs as its _BF16Linear
+ * (helix_substrate/basin_runtime.py:181-205).  in_features % 8 == 0 and <= 12288, ldw % 8 == 0,
+ * weight 16-byte aligned; y fp32, fp16 or bf16; fp32 accumulation.  The weight must be complete
+ * before the previous kernel on the stream started (it is fetched while that kernel drains). */
+int hxq_dense_gemv(const void* weight, int32_t out_features, int32_t in_features, int64_t ldw, const void* x,
+                   int32_t M, int64_t ldx, void* y, int y_dtype, int64_t ldy, hxq_stream_t stream);
+
 /*
  * ---- tensor-parallel sum after a row-parallel product, decode-sized messages ----
  * No counterpart in the reference (it has no multi-GPU path); replaces what

@@ -72,6 +72,7 @@ def test_glue_and_allreduce_entry_points_validate_without_a_device():
     assert L.hxq_add_rmsnorm(None, None, None, None, 1, 64, 64, 64, 64, 1e-6, None) == _lib.HXQ_E_ARG
     assert L.hxq_rope_append(None, 0, None, None, None, None, 0, None, None, 1, 4, 2, 64, 16, None) == _lib.HXQ_E_ARG
     assert L.hxq_swiglu(None, None, None, 1, 64, 64, 64, 64, None) == _lib.HXQ_E_ARG
+    assert L.hxq_dense_gemv(None, 8, 64, 64, None, 1, 64, None, 0, 8, None) == _lib.HXQ_E_ARG
     assert L.hxq_attn_decode(None, 0, None, None, None, None, 0, None, 0, 1, 4, 2, 64, 16, 0.125, None) == _lib.HXQ_E_ARG
     # sizes: 4-byte partial + 2 floats per (sequence, head, 64-row chunk); 2 slots x world x n_max floats
     assert L.hxq_attn_decode_workspace_bytes(2, 28, 128, 2184) == 2 * 28 * 35 * 130 * 4

@@ -93,6 +93,26 @@ def test_swiglu(B, n):
     assert rel_l2(out.float().cpu(), (F.silu(a) * b).float().cpu()) < 3e-3
 
 
+@pytest.mark.parametrize("n_out,n_in,M", [(1000, 3584, 1), (4097, 512, 2), (152064, 3584, 1), (999, 5120, 3), (64, 2056, 4)])
+def test_dense_gemv_against_fp64(n_out, n_in, M):
+    """hxq_dense_gemv (lm_head at decode time) against the fp64 product of the same bf16 operands:
+    fp32 accumulation, so only the summation order differs (rel-L2 <= 1e-5 for fp32 output); bf16
+    output is the rounded fp32 result; a padded weight stride and run-to-run equality."""
+    from helix_substrate_b200 import decode_ops
+    g = torch.Generator(device=_dev()).manual_seed(n_out + M)
+    pad = 8 if n_out < 5000 else 0
+    wfull = (0.02 * torch.randn(n_out, n_in + pad, device=_dev(), generator=g)).bfloat16()
+    w = wfull[:, :n_in]
+    x = torch.randn(M, n_in, device=_dev(), generator=g).bfloat16()
+    ref = x.double() @ w.double().t()
+    y32 = decode_ops.dense_gemv(w, x, out_dtype=torch.float32)
+    assert y32.shape == (M, n_out)
+    assert rel_l2(y32.double().cpu(), ref.cpu()) < 1e-5
+    yb = decode_ops.dense_gemv(w, x)
+    assert yb.dtype == torch.bfloat16 and torch.equal(yb, y32.bfloat16())
+    assert torch.equal(y32, decode_ops.dense_gemv(w, x, out_dtype=torch.float32))
+
+
 def test_glue_rejects_bad_arguments():
     from helix_substrate_b200 import _lib, decode_ops
     x = torch.zeros(2, 64, device=_dev(), dtype=torch.float32)

@@ -220,7 +220,7 @@ def test_workspace_survives_a_change_of_shape():
 
 @pytest.mark.parametrize("shape", [(18944, 3584), (3584, 18944), (4096, 4096)])
 def test_full_size_properties(shape):
-    """BASELINE shapes: (i) dequant equals an independent device-side gather,
+    """The benchmark shapes: (i) dequant equals an independent device-side gather,
     (ii) product equals dense fp64 matmul of the dequantised weight on a row
     sample, (iii) linearity in x, (iv) run-to-run bit equality."""
     n_out, n_in = shape
