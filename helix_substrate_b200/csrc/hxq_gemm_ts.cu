@@ -6,8 +6,9 @@
 // not like a GEMM: everything that is not a lookup is kept off the instruction stream of the warps
 // that do the lookups.
 //
-//   * CTA tile: 128 output rows x BN tokens (BN = 16, 32, 64, 128), K walked in stages of 128 columns,
-//     one CTA per SM; small row-tile grids split K over gridDim.z (fp32 partials + a fixed-order sum).
+//   * CTA tile: 128 output rows x BN tokens (BN = 16, 32, 64, 128), K walked in stages of one or two
+//     128-column boxes (two up to 32 tokens), one CTA per SM; small row-tile grids split K over
+//     gridDim.z (fp32 partials + a fixed-order sum).
 //   * index bytes: the 512 dequantising threads copy each stage's 128 x 128 box themselves with two
 //     16-byte asynchronous copies per thread (eight lanes per 128-byte line: whole lines per request)
 //     into a ring of up to eight 16 KB boxes laid out in the 128-byte swizzle, up to seven stages
@@ -56,15 +57,15 @@ void launch_splitk_reduce(const float* partial, int splits, int M, int out_featu
 namespace gemmts {
 
 constexpr int BM = 128;             // output rows per CTA = UMMA M = TMEM lanes
-constexpr int KS = 128;             // K columns per stage
+constexpr int KS = 128;             // K columns per index box (a stage is one or two boxes, see Rings)
 constexpr int DEQ_WARPS = 16;       // four warps per TMEM lane quarter, each takes 32 of a stage's 128 columns
 constexpr int DEQ_THREADS = 32 * DEQ_WARPS;
 constexpr int NUM_THREADS = 32 * (2 + DEQ_WARPS);   // activation producer, MMA issuer, 16 dequantisers
 constexpr int LUT_BYTES = 256 * 256;            // entry c, lane l at c * 256 + l * 4, base on a 64 KB boundary
-constexpr int IDX_BYTES = BM * KS;              // 16 KB
+constexpr int IDX_BYTES = BM * KS;              // 16 KB per box
 constexpr int SMEM_TOTAL = 232448;
 constexpr int TMEM_COLS = 512;
-constexpr int A_COLS = KS / 2;                  // 64 columns of packed bf16 pairs per stage
+constexpr int A_COLS = KS / 2;                  // 64 columns of packed bf16 pairs per box
 
 struct Args {
     const float* cb;
@@ -119,24 +120,32 @@ __device__ __forceinline__ uint32_t add_to_half(uint32_t pair, int hi, float del
 __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-// Ring depths per token tile: NB activation tiles / A-operand column blocks, NI index boxes.  The
-// table sits on a 64 KB boundary of the shared window, which leaves ~63 KB below and ~100 KB above it.
+// Per token tile: H index boxes (128 columns each) per stage, NB activation tiles / A-operand column
+// blocks, NI index boxes-of-a-stage.  Small token tiles take two boxes per stage: what a thread does
+// once per stage (barrier polls, the hand-over to the MMA warp, ring bookkeeping) is then paid once
+// per 64 instead of 32 weights; at 64 and 128 tokens the activation tiles leave no room for that.
+// The table sits on a 64 KB boundary of the shared window, which leaves ~63 KB below and ~100 KB above it.
 template <int BN> struct Rings;
-template <> struct Rings<16> { static constexpr int NB = 6, NI = 8; };
-template <> struct Rings<32> { static constexpr int NB = 5, NI = 7; };
-template <> struct Rings<64> { static constexpr int NB = 4, NI = 5; };
-template <> struct Rings<128> { static constexpr int NB = 3, NI = 3; };
+template <> struct Rings<16> { static constexpr int NB = 3, NI = 4, H = 2; };
+template <> struct Rings<32> { static constexpr int NB = 3, NI = 3, H = 2; };
+template <> struct Rings<64> { static constexpr int NB = 4, NI = 5, H = 1; };
+template <> struct Rings<128> { static constexpr int NB = 3, NI = 3, H = 1; };
+static int halves_of(int BN) { return BN <= 32 ? 2 : 1; }
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
-    constexpr int B_BYTES = BN * KS * 2;                 // two [BN x 64] bf16 sub-tiles
+    constexpr int H = Rings<BN>::H;                      // index boxes per stage
+    constexpr int KST = KS * H;                          // K columns per stage
+    constexpr int B_BYTES = BN * KST * 2;                // 2 H [BN x 64] bf16 sub-tiles
+    constexpr int IDXB = IDX_BYTES * H;                  // index bytes per stage
+    constexpr int ACOLS = A_COLS * H;                    // A-operand columns per stage
     constexpr int NB = Rings<BN>::NB;
     constexpr int NI = Rings<BN>::NI;
     // stages the index copies run ahead: one box of slack where the ring is deep enough, so that a warp
     // can start the next stage while the slowest warp is still reading the previous one
     constexpr int PD = NI >= 5 ? NI - 2 : NI - 1;
-    static_assert((BN < 32 ? 32 : BN) + NB * A_COLS <= TMEM_COLS, "accumulator + A ring must fit tensor memory");
+    static_assert((BN < 32 ? 32 : BN) + NB * ACOLS <= TMEM_COLS, "accumulator + A ring must fit tensor memory");
     static_assert(NI >= 2 && NI <= 8 && NB >= 2 && NB <= 6, "barrier and slot-table layout");
     extern __shared__ __align__(1024) char smem_raw[];
     const uint32_t smem_base = sm100::smem_u32(smem_raw);
@@ -146,8 +155,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
     // the table while they fit there, then the smaller ones in what is left below, the rest above.
     const uint32_t lo0 = (smem_base + 1023u) & ~1023u;
     const uint32_t hi0 = lut_base + LUT_BYTES;
-    constexpr bool B_FIRST = B_BYTES > IDX_BYTES;
-    constexpr uint32_t SZ1 = B_FIRST ? B_BYTES : IDX_BYTES, SZ2 = B_FIRST ? IDX_BYTES : B_BYTES;
+    constexpr bool B_FIRST = B_BYTES > IDXB;
+    constexpr uint32_t SZ1 = B_FIRST ? B_BYTES : IDXB, SZ2 = B_FIRST ? IDXB : B_BYTES;
     constexpr int N1 = B_FIRST ? NB : NI, N2 = B_FIRST ? NI : NB;
     const int room_lo = (int)(lut_base - lo0);
     const int n1_lo = room_lo / (int)SZ1 < N1 ? room_lo / (int)SZ1 : N1;
@@ -185,18 +194,18 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
     const bool row_ok = row < a.out_features;
     const bool affine = a.group_size > 0;
 
-    // ---- scale / offset of (row, this thread's 32 columns of stage ks)
-    // Staged case (one group per stage, fp32 tables with 16-byte aligned rows - every Qwen2.5 shape):
-    // the 128 rows' values for FOUR stages at a time ride with the index copies as one 16-byte
+    // ---- scale / offset of (row, this thread's 32 columns of a box)
+    // Staged case (one group per box, fp32 tables with 16-byte aligned rows - every Qwen2.5 shape):
+    // the 128 rows' values for FOUR boxes at a time ride with the index copies as one 16-byte
     // asynchronous copy per row and table into the unused halves of the codebook table's rows
     // (two buffers), and a thread picks its row's four values up with one 16-byte shared load.
     // A per-thread global load instead costs 32 cache-line look-ups per warp instruction, twice per
     // stage, on the same load/store pipe as the table lookups: it doubled the stage time.
     // Other layouts (fp16 tables, odd group sizes, shards starting mid-row-of-four) load per thread.
-    // (a K slice must start on a block of four stages: with two buffers, the third block's copy would
+    // (a K slice must start on a block of four boxes: with two buffers, the third block's copy would
     // otherwise be issued in the prologue, before the first block has been read)
     const bool st_staged = affine && a.group_size == KS && a.col0 % KS == 0 && a.st_dtype == HXQ_F32 &&
-                           a.ld_st % 4 == 0 && (KS0 & 3) == 0 &&
+                           a.ld_st % 4 == 0 && ((KS0 * H) & 3) == 0 &&
                            ((reinterpret_cast<uintptr_t>(a.scales) | reinterpret_cast<uintptr_t>(a.offsets)) & 15) == 0;
     const int g_base = affine ? a.col0 / a.group_size : 0;
     // hole h (16 bytes) of buffer b: entries [b][table][row], eight per table row, from table row 8 on
@@ -208,9 +217,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
     const bool sf_ok = st_staged && dt < 256 && o0 + sf_row < a.out_features;
     const float* sf_src = reinterpret_cast<const float*>(sf_which ? a.offsets : a.scales) +
                           (int64_t)(sf_ok ? o0 + sf_row : 0) * a.ld_st;
-    auto fetch_st4 = [&](int kj) {     // groups 4 B .. 4 B + 3 of the block B that stage kj belongs to
+    auto fetch_st4 = [&](int kj) {     // groups 4 B .. 4 B + 3 of the block B that stage kj's first box belongs to
         if (st_staged && dt < 256) {
-            const int blk = (KS0 + kj) >> 2;
+            const int blk = ((KS0 + kj) * H) >> 2;
             int n = a.n_groups - 4 * blk;
             n = n > 4 ? 4 : (n < 0 ? 0 : n);
             const uint32_t bytes = sf_ok ? (uint32_t)(4 * n) : 0u;
@@ -218,10 +227,10 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                          :: "r"(st_hole(blk & 1, sf_which, sf_row)), "l"(bytes ? sf_src + 4 * blk : reinterpret_cast<const float*>(a.scales)), "r"(bytes) : "memory");
         }
     };
-    auto load_st = [&](int ks, float& s, float& t) {     // the per-thread path
+    auto load_st = [&](int bx, float& s, float& t) {     // the per-thread path; bx: box number inside this K slice
         s = 1.f; t = 0.f;
         if (affine && row_ok) {
-            int g = (a.col0 + (KS0 + ks) * KS + kq * 32) / a.group_size - g_base;
+            int g = (a.col0 + (KS0 * H + bx) * KS + kq * 32) / a.group_size - g_base;
             g = g < a.n_groups ? g : a.n_groups - 1;      // K tail: those activations are zero
             const int64_t o = (int64_t)row * a.ld_st + g;
             if (a.st_dtype == HXQ_F32) {
@@ -234,27 +243,31 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
         }
     };
 
-    // ---- index copies.  Copy mapping (not the row this thread dequantises): chunk q = dt + 512 c,
+    // ---- index copies.  Copy mapping (not the row this thread dequantises), per box: chunk q = dt + 512 c,
     // c = 0, 1: box row q / 8, 16-byte piece q % 8 -> eight consecutive lanes fetch one 128-byte line.
     const int c_row = dt >> 3, c_piece = dt & 7;                 // second copy: row + 64, same piece
     const bool c_ok0 = o0 + c_row < a.out_features, c_ok1 = o0 + c_row + 64 < a.out_features;
-    const uint8_t* c_src0 = a.idx + (int64_t)(c_ok0 ? o0 + c_row : 0) * a.ld_idx + (int64_t)KS0 * KS + c_piece * 16;
-    const uint8_t* c_src1 = a.idx + (int64_t)(c_ok1 ? o0 + c_row + 64 : 0) * a.ld_idx + (int64_t)KS0 * KS + c_piece * 16;
+    const uint8_t* c_src0 = a.idx + (int64_t)(c_ok0 ? o0 + c_row : 0) * a.ld_idx + (int64_t)KS0 * KST + c_piece * 16;
+    const uint8_t* c_src1 = a.idx + (int64_t)(c_ok1 ? o0 + c_row + 64 : 0) * a.ld_idx + (int64_t)KS0 * KST + c_piece * 16;
     const uint32_t c_dst0 = (uint32_t)(c_row * 128) + ((uint32_t)(c_piece ^ (c_row & 7)) << 4);
     const uint32_t c_dst1 = c_dst0 + 64u * 128u;                 // (row + 64) & 7 == row & 7
-    // stages whose 128 columns lie inside the matrix; the copies of later ones are cut at the edge
-    const int full_stages = a.in_features / KS - KS0;
-    auto copy_stage = [&](int kj) {     // this thread's two pieces of stage kj into ring slot kj % NI
+    // stages whose columns all lie inside the matrix; the copies of later ones are cut at the edge
+    const int full_stages = a.in_features / KST - KS0;
+    auto copy_stage = [&](int kj) {     // this thread's 2 H pieces of stage kj into ring slot kj % NI
         if (kj < NK) {
-            if (kj == 0 || ((KS0 + kj) & 3) == 0) fetch_st4(kj);
-            const uint32_t box = idx_slot(kj % NI);
-            const bool in_k = kj < full_stages || (int64_t)(KS0 + kj) * KS + c_piece * 16 + 16 <= a.in_features;
-            // rows past the matrix and columns past its end are filled with zeros (source size 0)
-            const uint32_t n0 = (c_ok0 && in_k) ? 16u : 0u, n1 = (c_ok1 && in_k) ? 16u : 0u;
-            const int64_t off = (int64_t)kj * KS;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(box + c_dst0), "l"(n0 ? c_src0 + off : a.idx), "r"(n0) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(box + c_dst1), "l"(n1 ? c_src1 + off : a.idx), "r"(n1) : "memory");
-            // one of the box barrier's 512 expected arrivals, made when this thread's copies so far have landed
+            if (kj == 0 || (((KS0 + kj) * H) & 3) == 0) fetch_st4(kj);
+            const uint32_t slot = idx_slot(kj % NI);
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+                const int64_t off = (int64_t)kj * KST + h * KS;
+                const bool in_k = kj < full_stages || (int64_t)KS0 * KST + off + c_piece * 16 + 16 <= a.in_features;
+                // rows past the matrix and columns past its end are filled with zeros (source size 0)
+                const uint32_t n0 = (c_ok0 && in_k) ? 16u : 0u, n1 = (c_ok1 && in_k) ? 16u : 0u;
+                const uint32_t box = slot + (uint32_t)(h * IDX_BYTES);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(box + c_dst0), "l"(n0 ? c_src0 + off : a.idx), "r"(n0) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(box + c_dst1), "l"(n1 ? c_src1 + off : a.idx), "r"(n1) : "memory");
+            }
+            // one of the stage barrier's 512 expected arrivals, made when this thread's copies so far have landed
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(sm100::smem_u32(&idx_full[kj % NI])) : "memory");
         }
     };
@@ -330,8 +343,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                 if (!sm100::mbar_wait(&st_free[s], ph ^ 1u, abort_flag, 2000000000LL, 200u)) break;
                 char* bt = smem_raw + (b_slot(s) - smem_base);
                 sm100::mbar_arrive_expect_tx(&b_full[s], (uint32_t)B_BYTES);
-                sm100::tma_load_2d(bt, &map_x, &b_full[s], (KS0 + ks) * KS, m0);
-                sm100::tma_load_2d(bt + BN * 128, &map_x, &b_full[s], (KS0 + ks) * KS + 64, m0);
+#pragma unroll
+                for (int j = 0; j < 2 * H; ++j)       // 64-column sub-tiles
+                    sm100::tma_load_2d(bt + j * (BN * 128), &map_x, &b_full[s], (KS0 + ks) * KST + 64 * j, m0);
                 armed = ks + 1;
             }
             if (*abort_flag != 0) {
@@ -352,9 +366,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                 sm100::tc_fence_after_sync();
                 // B: sub-tile kk / 4 (64 K columns each), + 32 bytes (2 in descriptor units) per 16-column slice
                 const uint64_t db0 = sm100::make_desc_k_sw128(b_slot(s));
-                const uint32_t ta = tmem_a0 + (uint32_t)(s * A_COLS);
+                const uint32_t ta = tmem_a0 + (uint32_t)(s * ACOLS);
 #pragma unroll
-                for (int kk = 0; kk < KS / 16; ++kk) {
+                for (int kk = 0; kk < KST / 16; ++kk) {
                     const uint64_t db = db0 + (uint64_t)((kk >> 2) * (BN * 128 / 16) + 2 * (kk & 3));
                     umma_bf16_ts(tmem_base, ta + (uint32_t)(kk * 8), db, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
                 }
@@ -392,7 +406,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
             return a.deltas[sc_e0 + e];
         };
         float st_s_n = 1.f, st_t_n = 0.f;
-        if (!st_staged) load_st(0, st_s_n, st_t_n);
+        if (!st_staged) load_st(0, st_s_n, st_t_n);      // box 0
         float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), t4 = make_float4(0.f, 0.f, 0.f, 0.f);
         bool failed = false;          // one of this thread's bounded waits gave up (or saw the abort flag)
         int stored = -1;              // last stage whose tcgen05.st was issued and not yet handed over
@@ -417,93 +431,102 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
                 break;
             }
             if (ks == 0) {     // the staged sidecar has landed with the first box: position the cursor
-                const int k_first = KS0 * KS;
+                const int k_first = KS0 * KST;
                 while (e_cur < e_end && sc_col(e_cur) < k_first) ++e_cur;
                 nc = e_cur < e_end ? sc_col(e_cur) : 0x7fffffff;
             }
-            float sc, of;
-            if (st_staged) {
-                const int ak = KS0 + ks;
-                if (ks == 0 || (ak & 3) == 0) {
-                    const uint32_t hs = st_hole((ak >> 2) & 1, 0, r), ht = st_hole((ak >> 2) & 1, 1, r);
-                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(s4.x), "=f"(s4.y), "=f"(s4.z), "=f"(s4.w) : "r"(hs));
-                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t4.x), "=f"(t4.y), "=f"(t4.z), "=f"(t4.w) : "r"(ht));
-                }
-                const int q = ak & 3;
-                sc = q == 0 ? s4.x : (q == 1 ? s4.y : (q == 2 ? s4.z : s4.w));
-                of = q == 0 ? t4.x : (q == 1 ? t4.y : (q == 2 ? t4.z : t4.w));
-            } else {
-                sc = st_s_n; of = st_t_n;
-                if (ks + 1 < NK) load_st(ks + 1, st_s_n, st_t_n);
-            }
-            uint32_t w[8];
-            {
-                const uint32_t idx_row = idx_slot(ks % NI) + (uint32_t)(r * 128);
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {     // 16 codes per load: chunk 2 * kq + c of the row, swizzled by the row
-                    const uint32_t addr = idx_row + ((uint32_t)((2 * kq + c) ^ (r & 7)) << 4);
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3]) : "r"(addr));
-                }
-            }
-            // the codes are (on their way) in registers: the box can be refilled
-            __syncwarp();
-            if (lane == 0) sm100::mbar_arrive(&idx_free[ks % NI]);
-            uint32_t out[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                const uint32_t a0 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)((j & 3) << 4));
-                const uint32_t a1 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)(((j + 1) & 3) << 4));
-                float v0, v1;
-                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v0) : "r"(a0));
-                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v1) : "r"(a1));
-                out[j >> 1] = pack_bf16x2(fmaf(v0, sc, of), fmaf(v1, sc, of));
-            }
-            // sidecar entries of this row inside this stage: mine are patched into the packed registers
-            // (a jump per entry instead of a dynamically indexed register array), the others skipped
-            {
-                const int k_lo = (KS0 + ks) * KS + kq * 32;
-                const int k_st = (KS0 + ks + 1) * KS;
-                while (nc < k_st) {
-                    const int j = nc - k_lo;
-                    if (j >= 0 && j < 32) {
-                        const int hi = j & 1;
-                        const float nd = sc_delta(e_cur);
-                        switch (j >> 1) {
-                            case 0: out[0] = add_to_half(out[0], hi, nd); break;
-                            case 1: out[1] = add_to_half(out[1], hi, nd); break;
-                            case 2: out[2] = add_to_half(out[2], hi, nd); break;
-                            case 3: out[3] = add_to_half(out[3], hi, nd); break;
-                            case 4: out[4] = add_to_half(out[4], hi, nd); break;
-                            case 5: out[5] = add_to_half(out[5], hi, nd); break;
-                            case 6: out[6] = add_to_half(out[6], hi, nd); break;
-                            case 7: out[7] = add_to_half(out[7], hi, nd); break;
-                            case 8: out[8] = add_to_half(out[8], hi, nd); break;
-                            case 9: out[9] = add_to_half(out[9], hi, nd); break;
-                            case 10: out[10] = add_to_half(out[10], hi, nd); break;
-                            case 11: out[11] = add_to_half(out[11], hi, nd); break;
-                            case 12: out[12] = add_to_half(out[12], hi, nd); break;
-                            case 13: out[13] = add_to_half(out[13], hi, nd); break;
-                            case 14: out[14] = add_to_half(out[14], hi, nd); break;
-                            default: out[15] = add_to_half(out[15], hi, nd); break;
-                        }
-                    }
-                    ++e_cur;
-                    nc = e_cur < e_end ? sc_col(e_cur) : 0x7fffffff;
-                }
-            }
-            __syncwarp();
-            // the previous stage's store has had these lookups to complete
-            if (stored >= 0) hand_over();
-            // the A columns of this ring slot are free once the MMAs that read them NB stages ago have retired
+            const uint32_t slot = idx_slot(ks % NI);
             const int sb = ks % NB;
-            // (warp-uniform outcome: the store below is a whole-warp instruction)
-            if (ks >= NB && !__all_sync(0xffffffffu, sm100::mbar_wait(&st_free[sb], (uint32_t)(ks / NB - 1) & 1u, abort_flag))) {
-                failed = true;
-                break;
+#pragma unroll 1
+            for (int h = 0; h < H; ++h) {     // the stage's boxes, one after the other (not unrolled: code size)
+                const int bx = ks * H + h;            // box number inside this K slice
+                float sc, of;
+                if (st_staged) {
+                    const int ag = KS0 * H + bx;      // == the box's group number
+                    if (bx == 0 || (ag & 3) == 0) {
+                        const uint32_t hs = st_hole((ag >> 2) & 1, 0, r), ht = st_hole((ag >> 2) & 1, 1, r);
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(s4.x), "=f"(s4.y), "=f"(s4.z), "=f"(s4.w) : "r"(hs));
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t4.x), "=f"(t4.y), "=f"(t4.z), "=f"(t4.w) : "r"(ht));
+                    }
+                    const int q = ag & 3;
+                    sc = q == 0 ? s4.x : (q == 1 ? s4.y : (q == 2 ? s4.z : s4.w));
+                    of = q == 0 ? t4.x : (q == 1 ? t4.y : (q == 2 ? t4.z : t4.w));
+                } else {
+                    sc = st_s_n; of = st_t_n;
+                    if (bx + 1 < NK * H) load_st(bx + 1, st_s_n, st_t_n);
+                }
+                uint32_t w[8];
+                {
+                    const uint32_t idx_row = slot + (uint32_t)(h * IDX_BYTES + r * 128);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {     // 16 codes per load: chunk 2 * kq + c of the row, swizzled by the row
+                        const uint32_t addr = idx_row + ((uint32_t)((2 * kq + c) ^ (r & 7)) << 4);
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3]) : "r"(addr));
+                    }
+                }
+                if (h == H - 1) {     // the stage's codes are (on their way) in registers: its boxes can be refilled
+                    __syncwarp();
+                    if (lane == 0) sm100::mbar_arrive(&idx_free[ks % NI]);
+                }
+                uint32_t out[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const uint32_t a0 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)((j & 3) << 4));
+                    const uint32_t a1 = __byte_perm(w[j >> 2], lane_key, 0x7604u | (uint32_t)(((j + 1) & 3) << 4));
+                    float v0, v1;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v0) : "r"(a0));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v1) : "r"(a1));
+                    out[j >> 1] = pack_bf16x2(fmaf(v0, sc, of), fmaf(v1, sc, of));
+                }
+                // sidecar entries of this row inside this box: mine are patched into the packed registers
+                // (a jump per entry instead of a dynamically indexed register array), the others skipped
+                {
+                    const int k_lo = (KS0 * H + bx) * KS + kq * 32;
+                    const int k_st = (KS0 * H + bx + 1) * KS;
+                    while (nc < k_st) {
+                        const int j = nc - k_lo;
+                        if (j >= 0 && j < 32) {
+                            const int hi = j & 1;
+                            const float nd = sc_delta(e_cur);
+                            switch (j >> 1) {
+                                case 0: out[0] = add_to_half(out[0], hi, nd); break;
+                                case 1: out[1] = add_to_half(out[1], hi, nd); break;
+                                case 2: out[2] = add_to_half(out[2], hi, nd); break;
+                                case 3: out[3] = add_to_half(out[3], hi, nd); break;
+                                case 4: out[4] = add_to_half(out[4], hi, nd); break;
+                                case 5: out[5] = add_to_half(out[5], hi, nd); break;
+                                case 6: out[6] = add_to_half(out[6], hi, nd); break;
+                                case 7: out[7] = add_to_half(out[7], hi, nd); break;
+                                case 8: out[8] = add_to_half(out[8], hi, nd); break;
+                                case 9: out[9] = add_to_half(out[9], hi, nd); break;
+                                case 10: out[10] = add_to_half(out[10], hi, nd); break;
+                                case 11: out[11] = add_to_half(out[11], hi, nd); break;
+                                case 12: out[12] = add_to_half(out[12], hi, nd); break;
+                                case 13: out[13] = add_to_half(out[13], hi, nd); break;
+                                case 14: out[14] = add_to_half(out[14], hi, nd); break;
+                                default: out[15] = add_to_half(out[15], hi, nd); break;
+                            }
+                        }
+                        ++e_cur;
+                        nc = e_cur < e_end ? sc_col(e_cur) : 0x7fffffff;
+                    }
+                }
+                __syncwarp();
+                if (h == 0) {
+                    // the previous stage's stores have had these lookups to complete
+                    if (stored >= 0) hand_over();
+                    // the A columns of this ring slot are free once the MMAs that read them NB stages ago have retired
+                    // (warp-uniform outcome: the store below is a whole-warp instruction)
+                    if (ks >= NB && !__all_sync(0xffffffffu, sm100::mbar_wait(&st_free[sb], (uint32_t)(ks / NB - 1) & 1u, abort_flag))) {
+                        failed = true;
+                        break;
+                    }
+                    sm100::tc_fence_after_sync();
+                }
+                tmem_st_32x16(t_row + (uint32_t)(sb * ACOLS + h * A_COLS), out);
             }
-            sm100::tc_fence_after_sync();
-            tmem_st_32x16(t_row + (uint32_t)(sb * A_COLS), out);
+            if (failed) break;
             stored = ks;
         }
         if (stored >= 0) hand_over();
@@ -570,13 +593,13 @@ static int sm_count() {
 static int pick_bn(int M) { return M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)); }
 
 // K slices per output tile: enough CTAs to fill the GPU when the row-tile grid alone does not, at
-// least four stages each.
-static int pick_splits(int grid_m, int grid_o, int k_steps, int n_sm) {
+// least four boxes (512 columns) each.  k_boxes: 128-column boxes of the K range.
+static int pick_splits(int grid_m, int grid_o, int k_boxes, int n_sm) {
     const int tiles = grid_m * grid_o;
     if (tiles * 2 > n_sm) return 1;
     int s = n_sm / tiles;
     if (s > 8) s = 8;
-    if (s > k_steps / 4) s = k_steps / 4;
+    if (s > k_boxes / 4) s = k_boxes / 4;
     return s < 1 ? 1 : s;
 }
 
@@ -634,15 +657,17 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
     a.group_size = d->group_size; a.ld_st = d->ld_st; a.st_dtype = d->st_dtype;
     a.n_groups = d->group_size > 0 ? (d->col0 + d->in_features - 1) / d->group_size - d->col0 / d->group_size + 1 : 0;
     a.M = M; a.y_dtype = y_dtype;
-    a.k_steps = (d->in_features + KS - 1) / KS;
+    const int H = halves_of(BN), k_boxes = (d->in_features + KS - 1) / KS;
+    a.k_steps = (k_boxes + H - 1) / H;
     const int grid_o = (d->out_features + BM - 1) / BM;
     const int grid_m = (M + BN - 1) / BN;
-    int splits = pick_splits(grid_m, grid_o, a.k_steps, sm_count());
+    int splits = pick_splits(grid_m, grid_o, k_boxes, sm_count());
     a.k_per_split = a.k_steps;
     a.partial = nullptr;
     if (splits > 1 && split_ws && aligned_to(split_ws, 16) &&
         split_ws_bytes >= (size_t)splits * M * d->out_features * sizeof(float)) {
-        a.k_per_split = ((a.k_steps + splits - 1) / splits + 3) & ~3;   // whole blocks of four stages (scale/offset staging)
+        const int per_block = 4 / H;      // stages per block of four boxes (scale/offset staging works in such blocks)
+        a.k_per_split = ((a.k_steps + splits - 1) / splits + per_block - 1) / per_block * per_block;
         splits = (a.k_steps + a.k_per_split - 1) / a.k_per_split;   // no empty slice
         a.partial = reinterpret_cast<float*>(split_ws);
     } else {
