@@ -319,8 +319,11 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
         const int c_end = (warp + 1) * per < 256 ? (warp + 1) * per : 256;
         for (int c0 = warp * per; c0 < c_end; c0 += 32) {
             const float mine = (c0 + lane < c_end) ? a.cb[c0 + lane] : 0.f;
-            for (int k = 0; k < 32 && c0 + k < c_end; ++k)
-                *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = __shfl_sync(0xffffffffu, mine, k);
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {     // fixed trip count: the 32 broadcasts pipeline instead of one shuffle -> store at a time
+                const float v = __shfl_sync(0xffffffffu, mine, k);
+                if (c0 + k < c_end) *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = v;
+            }
         }
     }
     for (int i = threadIdx.x; i < a.rbl_max; i += blockDim.x) cnt_s[i] = 0u;
@@ -810,8 +813,11 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
         const int c_end = (warp + 1) * per < 256 ? (warp + 1) * per : 256;
         for (int c0 = warp * per; c0 < c_end; c0 += 32) {
             const float mine = (c0 + lane < c_end) ? a.cb[c0 + lane] : 0.f;
-            for (int k = 0; k < 32 && c0 + k < c_end; ++k)
-                *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = __shfl_sync(0xffffffffu, mine, k);
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {     // fixed trip count: the 32 broadcasts pipeline instead of one shuffle -> store at a time
+                const float v = __shfl_sync(0xffffffffu, mine, k);
+                if (c0 + k < c_end) *reinterpret_cast<float*>(lut + (c0 + k) * 256 + lane * 4) = v;
+            }
         }
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -976,29 +982,36 @@ gemv_lean_kernel(const __grid_constant__ CUtensorMap tmap, const GemvArgs a) {
 #undef HXQ_LEAN_LANDED
     __syncthreads();
 
-    // ---- add the chunks of each row block in chunk order; lane j owns value j = row * MP + token ----
+    // ---- add the chunks of each row block; lane j < RM owns value j = row * MP + token.  The 32 / RM
+    // lane groups each add every (32 / RM)-th chunk, then the groups' sums meet by shuffles: a fixed
+    // order (results stay bit-identical from run to run) at a quarter of the dependent additions for
+    // one token (37 chunks per row block in down_proj).
     const int rb_last = (U1 - 1) / nch;
     const bool has = lane < RM;
-    const int row_i = lane / MP, m_i = lane % MP;
+    constexpr int NG = 32 / RM;                 // lane groups
+    const int lg = lane / RM, lj = lane % RM;
+    const int row_i = lj / MP, m_i = lj % MP;
     for (int rbx = rb_first + warp; rbx <= rb_last; rbx += W) {
         const int rb_u0 = rbx * nch;
         const int lo = (U0 > rb_u0 ? U0 : rb_u0) - rb_u0;
         const int hi = (U1 < rb_u0 + nch ? U1 : rb_u0 + nch) - rb_u0;
         float v = 0.f;
-        if (has)
-            for (int c = lo; c < hi; ++c) v += part_s[(rb_u0 + c - S0) * RM + lane];
+        for (int c = lo + lg; c < hi; c += NG) v += part_s[(rb_u0 + c - S0) * RM + lj];
+#pragma unroll
+        for (int off = RM; off < 32; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         if (hi - lo < nch) {   // cut by the CTA boundary: parts meet in global scratch
             const int c_first = cta_of_unit(a.units, gridDim.x, rb_u0);
             const int n_parts = cta_of_unit(a.units, gridDim.x, rb_u0 + nch - 1) - c_first + 1;
             float* sp = a.scratch + (int64_t)rbx * a.max_parts * RM;
             if (has) __stcg(sp + ((int)blockIdx.x - c_first) * RM + lane, v);
-            __threadfence();
+            // One release/acquire arrival per warp instead of fence + atomic + fence: the warp barrier orders
+            // the lanes' stores before lane 0's release, and lane 0's acquire before the lanes' loads below.
             __syncwarp();
             unsigned int g = 0;
-            if (lane == 0) g = atomicAdd(a.counters + rbx, 1u);
+            if (lane == 0)
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(g) : "l"(a.counters + rbx) : "memory");
             g = __shfl_sync(0xffffffffu, g, 0);
             if (g != (unsigned int)(n_parts - 1)) continue;
-            __threadfence();
             v = 0.f;
             if (has)
                 for (int q = 0; q < n_parts; ++q) {
