@@ -504,8 +504,12 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 // ---- lean kernel: shapes where every unit is whole ---------------------------------------
 //
 // OUT % 8 == 0, IN % 128 == 0, no column offset inside a group, group size 0 or 128, 16-byte
-// aligned activations: no unit touches an edge, so the per-unit code carries no bounds logic
-// at all.  Same unit, table and butterfly as gemv_kernel; what differs is the bookkeeping:
+// aligned activations: no unit touches a row edge, so the per-unit code carries no bounds logic
+// at all.  Template parameters: MP tokens per launch, XDT activation type, STM scale/offset
+// (0 none, 1 fp32, 2 fp16), SIDE "the matrix has a sidecar", TAIL "the last chunk of a row is
+// shorter than 512 columns" (whole 128-column groups; its lanes past the end fetch lane 0's
+// addresses and hold zero activations) - as run-time switches they cost 2-6 % per launch.
+// Same unit, table and butterfly as gemv_kernel; what differs is the bookkeeping:
 //  * index bytes travel global -> shared with 16-byte asynchronous copies (each lane copies, and
 //    later reads back, its own 16 bytes of each of the 8 rows: a per-warp double buffer of two
 //    4 KB units that needs no synchronisation beyond the copy-group wait).  Register loads for
@@ -520,9 +524,10 @@ __global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const
 //    slot offset, each advanced by a warp-uniform delta),
 //  * a unit ends with ONE store of its 8 x M partial sums into its own shared-memory slot;
 //    there are no arrival counters inside the CTA.  After the last unit the CTA meets at one
-//    barrier and the warps add the slots of each row block in chunk order (deterministic),
-//    then store y - or, for a row block cut by the CTA boundary, go through the same global
-//    scratch + arrival counter as gemv_kernel.
+//    barrier and the warps add the slots of each row block in a fixed order (deterministic; the
+//    lane groups of a warp each take every n-th chunk and meet by shuffles), then store y - or,
+//    for a row block cut by the CTA boundary, go through global scratch + an arrival counter
+//    (one release/acquire atomic per warp; the last arriver adds the parts in CTA order).
 constexpr int kLeanSmemBytes = 232448;          // all of the SM's shared memory: table + slots + index rings
 constexpr int kLeanCarriers = 8;                // units of a row block that share its sidecar
 
