@@ -87,6 +87,9 @@ template <int MP>
 struct GemvCfg {
     static constexpr int kMaxWarps = (MP == 1) ? HXQ_GEMV_W1 : 12;   // (four tokens: 168 registers at 12 warps, 4 % faster than 8 warps at 255)
     static constexpr int kMaxThreads = 32 * kMaxWarps;
+    // the edge-tolerant kernel holds more state per lane: at four tokens it spills above 8 warps
+    static constexpr int kEdgeMaxWarps = (MP == 4) ? 8 : kMaxWarps;
+    static constexpr int kEdgeMaxThreads = 32 * kEdgeMaxWarps;
 };
 
 // What a warp fetches one unit ahead of consuming it.
@@ -200,7 +203,7 @@ __device__ __forceinline__ float sum2(uint64_t v) {
 }
 
 template <int MP>
-__global__ void __launch_bounds__(GemvCfg<MP>::kMaxThreads, 1) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GemvCfg<MP>::kEdgeMaxThreads, 1) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(1024) char dyn_smem[];
     constexpr int RM = kRows * MP;
     const int lane = threadIdx.x & 31;
@@ -1328,10 +1331,15 @@ int gemv_any_m(const hxq_desc* d, const void* x, int x_dtype, int32_t M, int64_t
         if (lean) lean = gemv_index_map(&tmap, d);
         a.slot_bytes = lean ? lean_slot_bytes(p, MP) : 0;
         a.tail_lanes = (lean && d->in_features % kChunk) ? (d->in_features % kChunk) / 16 : 32;
+        if (!lean) {     // the other kernel's warp limit
+            pl = p;
+            const int wedge = (MP == 4) ? GemvCfg<4>::kEdgeMaxWarps : (MP == 2 ? GemvCfg<2>::kEdgeMaxWarps : GemvCfg<1>::kEdgeMaxWarps);
+            if (pl.warps_per_cta > wedge) pl.warps_per_cta = wedge;
+        }
         int st;
-        if (MP == 1) st = launch_fast<1>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
-        else if (MP == 2) st = launch_fast<2>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
-        else st = launch_fast<4>(a, lean ? pl : p, lean ? &tmap : nullptr, stream);
+        if (MP == 1) st = launch_fast<1>(a, pl, lean ? &tmap : nullptr, stream);
+        else if (MP == 2) st = launch_fast<2>(a, pl, lean ? &tmap : nullptr, stream);
+        else st = launch_fast<4>(a, pl, lean ? &tmap : nullptr, stream);
         if (st != HXQ_OK) return st;
         m0 += mm;
     }
