@@ -49,7 +49,7 @@ class HelixLinear(nn.Module):
     """y = x @ W^T + bias with W held as codebook + uint8 indices + sidecar
     (+ optional group affine, SVD residual and AWQ channel scales)."""
 
-    _shared_buffer = None      # kept for attribute compatibility; never allocated
+    _shared_buffer = None      # bf16 / fp16 scratch of the buffered mode, one per process, sized to the largest layer seen
     _shared_buffer_size = 0
 
     def __init__(self, in_features: int, out_features: int, codebook: torch.Tensor, indices: torch.Tensor,
@@ -96,7 +96,10 @@ class HelixLinear(nn.Module):
         self._sidecar_apply_count = self._sidecar_skip_count = 0
         self._sidecar_norms = []
         self._cuda_graph_mode = False
-        self._forward_mode = "fused"   # accepted values: buffered | fused | naive; all run the CUDA path
+        # "fused" (default) and "naive": the fused sm_100a kernels.  "buffered": the reference's default mode
+        # (helix_linear.py:556-634) - the whole weight dequantised into a shared 16-bit buffer by hxq_dequant,
+        # then one dense library GEMM; worth choosing for prefill beyond ~1000 tokens.
+        self._forward_mode = "fused"
         self._weight_buffer = None
         self._wave_enabled = False
         self.index_packing = None
@@ -279,8 +282,8 @@ class HelixLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x[..., in] -> y[..., out] in x's dtype (helix_linear.py:318-361).
-        ``_forward_mode`` is accepted for compatibility; every value runs the
-        same CUDA kernels."""
+        ``_forward_mode`` "buffered" selects the two-pass path (see ``_forward_buffered``); every
+        other value runs the fused kernels."""
         if not x.is_cuda:
             raise RuntimeError(
                 "HelixLinear.forward got a CPU tensor: this build has CUDA kernels only "
@@ -288,6 +291,9 @@ class HelixLinear(nn.Module):
         if self._kurtosis_gate is not None and self.has_svd:
             with torch.no_grad():
                 self._cell_skip_svd = not self._kurtosis_gate.step(x, cuda_graph_safe=self._cuda_graph_mode)
+        if getattr(self, "_forward_mode", "fused") == "buffered":
+            self._last_dispatch_path = "buffered"
+            return self._forward_buffered(x)
         self._last_dispatch_path = "fused"
         return self._run(x, x.dtype if x.dtype in (torch.float16, torch.bfloat16, torch.float32) else torch.float32)
 
@@ -318,8 +324,35 @@ class HelixLinear(nn.Module):
         return self._run(x, torch.float32)
 
     _forward_naive = _forward_fused
-    _forward_buffered = _forward_fused
     _forward_wave = _forward_fused
+
+    def _forward_buffered(self, x: torch.Tensor) -> torch.Tensor:
+        """The reference's buffered mode (helix_linear.py:556-634): materialise the whole weight in a
+        16-bit buffer shared by all modules, then one dense matmul.  The materialisation is
+        ``hxq_dequant`` (codebook, group affine and sidecar in one pass over the indices: 3 bytes of
+        traffic per weight where the reference's gather chain moves ~17); the matmul is the
+        framework's dense GEMM, as in the reference.  Result in x's dtype (bf16 compute for fp32 x)."""
+        if not x.is_cuda:
+            raise RuntimeError("HelixLinear._forward_buffered got a CPU tensor. No silent fallback.")
+        shape = x.shape
+        x2 = x.reshape(-1, self.in_features)
+        if self.has_channel_scales:
+            x2 = x2 / self.channel_scales.to(x2.dtype).unsqueeze(0)
+        compute_dt = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
+        needed = self.out_features * self.in_features
+        buf = HelixLinear._shared_buffer
+        if buf is None or buf.device != x.device or buf.dtype != compute_dt or HelixLinear._shared_buffer_size < needed:
+            buf = torch.empty(needed, dtype=compute_dt, device=x.device)
+            HelixLinear._shared_buffer, HelixLinear._shared_buffer_size = buf, needed
+        w = buf[:needed].view(self.out_features, self.in_features)
+        apply_sc = self._policy_decide(x2) if self._csr_rowptr is not None else False
+        self.packed(with_sidecar=apply_sc).dequant(dtype=compute_dt, out=w)
+        if self.has_svd and not self._cell_skip_svd:
+            w += ((self.svd_U * self.svd_s.unsqueeze(0)) @ self.svd_Vt).to(compute_dt)
+        bias = None if self.bias is None else self.bias.to(compute_dt)
+        y = torch.nn.functional.linear(x2.to(compute_dt), w, bias)
+        self._last_dispatch = {"dispatch_selected": "hxq_dequant_sm100a+dense_gemm", "tokens": int(x2.shape[0]), "vq_dim": 1}
+        return y.to(x.dtype if x.dtype in (torch.float16, torch.bfloat16, torch.float32) else torch.float32).reshape(*shape[:-1], self.out_features)
 
     def _dequant_tile(self, start_row: int, end_row: int) -> torch.Tensor:
         """Rows [start_row, end_row) as dense fp32 on the GPU.  Sidecar entries

@@ -121,6 +121,34 @@ def test_sidecar_policy_and_svd_and_channel_scales():
         mod.set_sidecar_policy("sometimes")
 
 
+@pytest.mark.parametrize("xdt", [torch.bfloat16, torch.float16, torch.float32])
+def test_buffered_mode_is_dequant_plus_dense_gemm(xdt):
+    """_forward_mode = "buffered" (the reference's default mode, helix_linear.py:556-634): the weight
+    materialised by hxq_dequant into the shared 16-bit buffer, then a dense matmul.  Against the fp64
+    product of the bit-exact dequantised weight (16-bit operands: rel-L2 <= 1e-2), against the fused
+    mode, with a group affine, a sidecar and a bias; the buffer is shared by modules of any size."""
+    from helix_substrate_b200 import HelixLinear
+    from helix_substrate_b200.hxq_writer_gpu import compress_weight, student_t_weight
+    mods = []
+    for i, (n_out, n_in) in enumerate([(384, 1024), (200, 512)]):
+        enc = compress_weight(student_t_weight((n_out, n_in), 40 + i, DEV), percentile=99.9, group_size=128)
+        mods.append(HelixLinear(n_in, n_out, bias=torch.randn(n_out, device=DEV) * 0.02, **enc).to(DEV))
+    for mod in mods:
+        x = torch.randn(3, 50, mod.in_features, device=DEV).to(xdt)
+        ref = x.double() @ mod.decode_weight().double().t() + mod.bias.double()
+        y_fused = mod(x)
+        mod._forward_mode = "buffered"
+        y = mod(x)
+        assert mod._last_dispatch_path == "buffered" and mod.dispatch_metadata()["dispatch_path"] == "buffered"
+        assert y.shape == (3, 50, mod.out_features) and y.dtype == xdt
+        assert rel_l2(y.double().cpu().numpy(), ref.cpu().numpy()) < 1e-2
+        assert rel_l2(y.double().cpu().numpy(), y_fused.double().cpu().numpy()) < 1.5e-2
+        assert torch.equal(y, mod(x))
+        mod._forward_mode = "fused"
+        assert torch.equal(mod(x), y_fused)
+    assert HelixLinear._shared_buffer_size >= 384 * 1024
+
+
 def test_swap_to_helix_and_summary(tmp_path):
     from helix_substrate_b200 import swap_to_helix, swap_summary, HelixLinear
     g = load_golden("vq_sidecar_64x32")
