@@ -190,6 +190,82 @@ def test_hf_round_trip_builds_shells_and_keeps_rope(tmp_path):
     assert torch.allclose(loaded.model.rotary_emb.inv_freq, inv_ref)
 
 
+def test_cdnav3_directory_to_hf_checkpoint_with_completeness_gate(tmp_path):
+    """dense model on disk -> CDNAv3Writer folders -> convert_model -> from_pretrained: the compressed
+    linears come back as HelixLinear holding exactly what the folders hold (codebook, indices,
+    sidecar, group affine), everything the writer skipped is copied from the dense checkpoint in
+    its own dtype, and a dense tensor that is neither copied nor replaced stops the conversion."""
+    transformers = pytest.importorskip("transformers")
+    from safetensors.torch import load_file, save_file
+    import helix_substrate  # noqa: F401  registers the quantizer
+    from helix_substrate_b200 import HelixLinear
+    from helix_substrate_b200.cdnav3_writer import CDNAv3Writer
+    from helix_substrate_b200.cdnav3_reader import CDNAv3Reader
+    from helix_substrate_b200.convert_safetensors import convert_cdnav3_to_safetensors, convert_model
+    from helix_substrate_b200.tensor_policy import TensorClass, TensorPolicy
+    cfg = transformers.Qwen2Config(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                   rope_theta=1e6, tie_word_embeddings=False)
+    torch.manual_seed(1)
+    dense = transformers.Qwen2ForCausalLM(cfg).eval()
+    dense_dir = tmp_path / "dense"
+    dense.save_pretrained(dense_dir, safe_serialization=True)
+    w = CDNAv3Writer(tmp_path / "cdnav3")
+    pol = TensorPolicy(TensorClass.FFN, "codebook+sidecar", percentile=99.0, max_corrections=0, group_size=64)
+    pol_plain = TensorPolicy(TensorClass.ATTENTION_QK, "codebook+sidecar", percentile=99.0, max_corrections=0)
+    names = []
+    for name, m in dense.named_modules():
+        if isinstance(m, nn.Linear) and name != "lm_head":
+            w.write_tensor(m.weight.detach().numpy(), name + ".weight", pol if "mlp" in name else pol_plain)
+            names.append(name)
+    w.write_tensor(dense.model.norm.weight.detach().numpy(), "model.norm.weight")      # an exact 1-D tensor
+    stats = convert_model(tmp_path / "cdnav3", dense_dir, tmp_path / "hf")
+    assert stats["n_compressed"] == len(names) == 7 and stats["n_exact"] == 1 and stats["group_size"] == 64
+    assert sorted(stats["compressed_modules"]) == sorted(names)
+    ck = load_file(str(tmp_path / "hf" / "model.safetensors"))
+    sd = dense.state_dict()
+    for k, v in sd.items():        # every dense tensor: itself, or replaced by its parts
+        if k[:-len(".weight")] in names and k.endswith(".weight"):
+            assert k not in ck and k[:-7] + ".codebook" in ck and ck[k[:-7] + ".indices"].shape == v.shape
+        elif k != "model.norm.weight":
+            assert torch.equal(ck[k], v), k
+    assert ck["model.norm.weight"].dtype == torch.float16          # the writer's exact tensors are fp16
+    qc = json.loads((tmp_path / "hf" / "config.json").read_text())["quantization_config"]
+    assert qc["quant_method"] == "cdna_v3" and qc["group_size"] == 64 and sorted(qc["compressed_modules"]) == sorted(names)
+    assert json.loads((tmp_path / "hf" / "conversion_receipt.json").read_text())["n_total_keys"] == len(ck)
+    loaded = transformers.AutoModelForCausalLM.from_pretrained(tmp_path / "hf")
+    n = 0
+    for name, m in loaded.named_modules():
+        if isinstance(m, HelixLinear):
+            n += 1
+            d = tmp_path / "cdnav3" / (name.replace(".", "_") + "_weight.cdnav3")
+            assert torch.equal(m.codebook[: 256], torch.from_numpy(np.load(d / "codebook.npy")))
+            assert np.array_equal(m.indices.numpy().ravel(), np.fromfile(d / "indices.bin", dtype=np.uint8))
+            assert (m.group_size == 64) == ("mlp" in name)
+            if "mlp" in name:
+                assert torch.equal(m.group_scales, torch.from_numpy(np.load(d / "group_scales.npy")))
+    assert n == 7 and isinstance(loaded.lm_head, nn.Linear)
+    assert torch.equal(loaded.model.embed_tokens.weight, dense.model.embed_tokens.weight)
+    # the gate: a folder that claims gate_proj but holds a matrix of another shape (a stale folder from
+    # another model) and an exact tensor of the wrong size both stop the conversion
+    import shutil
+    stale = tmp_path / "cdnav3_stale"
+    shutil.copytree(tmp_path / "cdnav3", stale)
+    shutil.rmtree(stale / "model_layers_0_mlp_gate_proj_weight.cdnav3")
+    CDNAv3Writer(stale).write_tensor(np.random.default_rng(0).standard_normal((64, 32)).astype(np.float32),
+                                     "model.layers.0.mlp.gate_proj.weight", pol_plain)
+    with pytest.raises(RuntimeError, match="completeness gate"):
+        convert_cdnav3_to_safetensors(stale, tmp_path / "x.safetensors", dense_dir)
+    wrong = tmp_path / "cdnav3_wrong"
+    shutil.copytree(tmp_path / "cdnav3", wrong)
+    CDNAv3Writer(wrong).write_tensor(np.ones(7, np.float32), "model.norm.weight")
+    with pytest.raises(RuntimeError, match="completeness gate"):
+        convert_cdnav3_to_safetensors(wrong, tmp_path / "y.safetensors", dense_dir)
+    # without a dense checkpoint to compare with, the folders alone convert
+    alone = convert_cdnav3_to_safetensors(tmp_path / "cdnav3", tmp_path / "z.safetensors")
+    assert alone["n_from_original"] == 0 and alone["n_total_keys"] < len(ck)
+
+
 def test_per_tensor_affine_reference_formula_on_cpu():
     """affine_matmul_reference (any device) is the dense product with W = idx * step + offset."""
     import numpy as np
