@@ -7,7 +7,7 @@
 // that do the lookups.
 //
 //   * CTA tile: 128 output rows x BN tokens (BN = 16, 32, 64, 128), K walked in stages of one or two
-//     128-column boxes (two up to 32 tokens), one CTA per SM; small row-tile grids split K over
+//     128-column boxes (two up to 64 tokens), one CTA per SM; small row-tile grids split K over
 //     gridDim.z (fp32 partials + a fixed-order sum).
 //   * index bytes: the 512 dequantising threads copy each stage's 128 x 128 box themselves with two
 //     16-byte asynchronous copies per thread (eight lanes per 128-byte line: whole lines per request)
@@ -121,16 +121,17 @@ __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // Per token tile: H index boxes (128 columns each) per stage, NB activation tiles / A-operand column
-// blocks, NI index boxes-of-a-stage.  Small token tiles take two boxes per stage: what a thread does
-// once per stage (barrier polls, the hand-over to the MMA warp, ring bookkeeping) is then paid once
-// per 64 instead of 32 weights; at 64 and 128 tokens the activation tiles leave no room for that.
+// blocks, NI index boxes-of-a-stage.  Up to 64 tokens a stage is two boxes: what a thread does once
+// per stage (barrier polls, the hand-over to the MMA warp, ring bookkeeping) is then paid once per
+// 64 instead of 32 weights, and the two boxes' lookups overlap each other's tails (at 64 tokens
+// even with rings of two: 76 vs 89 us); at 128 tokens the activation tiles leave no room for that.
 // The table sits on a 64 KB boundary of the shared window, which leaves ~63 KB below and ~100 KB above it.
 template <int BN> struct Rings;
 template <> struct Rings<16> { static constexpr int NB = 3, NI = 4, H = 2; };
 template <> struct Rings<32> { static constexpr int NB = 3, NI = 3, H = 2; };
-template <> struct Rings<64> { static constexpr int NB = 4, NI = 5, H = 1; };
+template <> struct Rings<64> { static constexpr int NB = 2, NI = 2, H = 2; };
 template <> struct Rings<128> { static constexpr int NB = 3, NI = 3, H = 1; };
-static int halves_of(int BN) { return BN <= 32 ? 2 : 1; }
+static int halves_of(int BN) { return BN <= 64 ? 2 : 1; }
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -437,8 +438,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap map_x, const Args a) {
             }
             const uint32_t slot = idx_slot(ks % NI);
             const int sb = ks % NB;
-#pragma unroll 1
-            for (int h = 0; h < H; ++h) {     // the stage's boxes, one after the other (not unrolled: code size)
+#pragma unroll
+            for (int h = 0; h < H; ++h) {     // the stage's boxes; unrolled, so that the second box's code loads and lookups
+                                              // are scheduled into the first one's patching and store (7 % at 32 tokens)
                 const int bx = ks * H + h;            // box number inside this K slice
                 float sc, of;
                 if (st_staged) {
