@@ -61,9 +61,16 @@ template <int BN> struct Smem {
     static constexpr int BNS = BN / NSUB;             // tokens per accumulator
     static constexpr int STAGES = BN > 256 ? 2 : (BN == 256 ? 3 : (BN == 128 ? 4 : 6));   // as deep as shared memory allows
     static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + IDX_BYTES;
-    static constexpr int BAR_OFFSET = LUT_BYTES + STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // dequantised weight tile + activation tiles
+    // The index boxes have a ring of their own, deeper than the stages: they come from HBM and are
+    // consumed by the dequantising warps long before the stage's MMAs retire.  (With the box inside the
+    // stage, a two-stage kernel had the HBM round trip of the indices in series with dequantisation
+    // and the MMAs of every stage.)
+    static constexpr int NIDX = BN > 256 ? 4 : (BN == 256 ? 6 : (BN == 128 ? 8 : 6));
+    static constexpr int IDX_OFFSET = LUT_BYTES + STAGES * STAGE_BYTES;
+    static constexpr int BAR_OFFSET = IDX_OFFSET + NIDX * IDX_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;  // barriers + slack for 1024-byte alignment
+    static_assert(TOTAL <= 232448, "stages + index ring must fit one SM's shared memory");
 };
 
 struct GemmArgs {
@@ -99,11 +106,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
     char* lut = smem;
     char* stage0 = smem + LUT_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
-    uint64_t* tma_full = bars;                  // [STAGES] index + activation bytes landed
+    constexpr int NIDX = S::NIDX;
+    char* idx0 = smem + S::IDX_OFFSET;
+    uint64_t* b_full = bars;                    // [STAGES] activation tiles landed
     uint64_t* a_full = bars + STAGES;           // [STAGES] bf16 weight tile written
-    uint64_t* empty = bars + 2 * STAGES;        // [STAGES] UMMAs of the stage retired
-    uint64_t* acc_full = bars + 3 * STAGES;     // accumulator complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    uint64_t* empty = bars + 2 * STAGES;        // [STAGES] UMMAs of the stage retired: its A and B tiles are free
+    uint64_t* idx_full = bars + 3 * STAGES;     // [NIDX] index box landed
+    uint64_t* idx_free = idx_full + NIDX;       // [NIDX] index box read by every dequantising warp
+    uint64_t* acc_full = idx_free + NIDX;       // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    static_assert((3 * 6 + 2 * 8 + 2) * 8 <= 512, "barrier area");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -116,9 +128,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            sm100::mbar_init(&tma_full[s], 1);
+            sm100::mbar_init(&b_full[s], 1);
             sm100::mbar_init(&a_full[s], NUM_DEQ_WARPS);
             sm100::mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < NIDX; ++s) {
+            sm100::mbar_init(&idx_full[s], 1);
+            sm100::mbar_init(&idx_free[s], NUM_DEQ_WARPS);
         }
         sm100::mbar_init(acc_full, 1);
         *abort_flag = 0;
@@ -141,23 +157,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int armed = 0;
+            int armed = 0, armed_idx = 0;
+            auto load_idx = [&](int ki) {      // index box of stage ki into ring slot ki % NIDX
+                const int si = ki % NIDX;
+                sm100::mbar_arrive_expect_tx(&idx_full[si], (uint32_t)IDX_BYTES);
+                sm100::tma_load_2d(idx0 + si * IDX_BYTES, &map_idx, &idx_full[si], (KS0 + ki) * BK, o0);
+                armed_idx = ki + 1;
+            };
+            for (int ki = 0; ki < NIDX - 1 && ki < KS; ++ki) load_idx(ki);
             for (int ks = 0; ks < KS; ++ks) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
                 if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                 char* st = stage0 + s * S::STAGE_BYTES;
-                sm100::mbar_arrive_expect_tx(&tma_full[s], (uint32_t)(IDX_BYTES + S::B_BYTES));
-                sm100::tma_load_2d(st + A_BYTES + S::B_BYTES, &map_idx, &tma_full[s], (KS0 + ks) * BK, o0);
+                sm100::mbar_arrive_expect_tx(&b_full[s], (uint32_t)S::B_BYTES);
 #pragma unroll
                 for (int n = 0; n < S::NSUB; ++n)
-                    sm100::tma_load_2d(st + A_BYTES + n * (S::BNS * BK * 2), &map_x, &tma_full[s], (KS0 + ks) * BK, m0 + n * S::BNS);
+                    sm100::tma_load_2d(st + A_BYTES + n * (S::BNS * BK * 2), &map_x, &b_full[s], (KS0 + ks) * BK, m0 + n * S::BNS);
                 armed = ks + 1;
+                // then the index box NIDX - 1 stages ahead: its slot held stage ks - 1
+                const int ki = ks + NIDX - 1;
+                if (ki < KS) {
+                    if (ks >= 1 && !sm100::mbar_wait(&idx_free[ki % NIDX], (uint32_t)(ki / NIDX - 1) & 1u, abort_flag)) break;
+                    load_idx(ki);
+                }
             }
             if (*abort_flag != 0) {
                 // gave up: let copies already in flight land before the CTA retires
                 for (int ks = (armed > STAGES ? armed - STAGES : 0); ks < armed; ++ks)
-                    sm100::mbar_wait(&tma_full[ks % STAGES], (uint32_t)(ks / STAGES) & 1u, abort_flag, 200000000LL);
+                    sm100::mbar_wait(&b_full[ks % STAGES], (uint32_t)(ks / STAGES) & 1u, abort_flag, 200000000LL);
+                for (int ki = (armed_idx > NIDX ? armed_idx - NIDX : 0); ki < armed_idx; ++ki)
+                    sm100::mbar_wait(&idx_full[ki % NIDX], (uint32_t)(ki / NIDX) & 1u, abort_flag, 200000000LL);
             }
         }
     } else if (warp == 1) {
@@ -168,7 +198,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
             for (int ks = 0; ks < KS && ok; ++ks) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-                ok = sm100::mbar_wait(&tma_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
+                ok = sm100::mbar_wait(&b_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
                 if (!ok) break;
                 sm100::tc_fence_after_sync();
                 char* st = stage0 + s * S::STAGE_BYTES;
@@ -241,9 +271,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
 #pragma unroll
                 for (int p = 0; p < PASSES; ++p) load_st(ks + 1, o0 + r_a + 8 * p, sc_n[p], of_n[p]);
             }
-            if (!sm100::mbar_wait(&tma_full[s], ph, abort_flag)) break;
+            const int si = ks % NIDX;
+            // the stage's index box has landed, and the A tile of this stage slot is free (the MMAs that read it
+            // STAGES steps ago have retired; parity 1 on a fresh barrier passes at once)
+            if (!sm100::mbar_wait(&idx_full[si], (uint32_t)(ks / NIDX) & 1u, abort_flag)) break;
+            if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
             char* st = stage0 + s * S::STAGE_BYTES;
-            const char* idx_s = st + A_BYTES + S::B_BYTES;
+            const char* idx_s = idx0 + si * IDX_BYTES;
 
 #pragma unroll
             for (int pass = 0; pass < PASSES; ++pass) {
@@ -294,7 +328,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
             }
             sm100::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) sm100::mbar_arrive(&a_full[s]);
+            if (lane == 0) {
+                sm100::mbar_arrive(&idx_free[si]);     // the box has been read (sidecar patch included)
+                sm100::mbar_arrive(&a_full[s]);
+            }
         }
 
         // ------------------------------------------------------------ epilogue (all dequantising warps)
