@@ -53,21 +53,26 @@ constexpr int IDX_BYTES = BM * BK;     // 8 KB
 constexpr int NUM_DEQ_WARPS = HXQ_GEMM_DEQ_WARPS;          // 8 or 16
 constexpr int ROWS_PER_WARP = BM / NUM_DEQ_WARPS;           // 16 or 8
 constexpr int PASSES = ROWS_PER_WARP / 8;                   // a warp covers 8 rows x 64 columns per pass
-constexpr int NUM_THREADS = 32 * (2 + NUM_DEQ_WARPS);
+constexpr int NUM_THREADS = 32 * (3 + NUM_DEQ_WARPS);   // activation producer, MMA issuer, dequantisers, index producer
 static_assert(NUM_DEQ_WARPS == 8 || NUM_DEQ_WARPS == 16, "dequantising warps: 8 or 16");
 
 template <int BN> struct Smem {
     static constexpr int NSUB = BN > 256 ? 2 : 1;     // accumulators (UMMA N <= 256)
     static constexpr int BNS = BN / NSUB;             // tokens per accumulator
-    static constexpr int STAGES = BN > 256 ? 2 : (BN == 256 ? 3 : (BN == 128 ? 4 : 6));   // as deep as shared memory allows
+    static constexpr int STAGES = BN > 256 ? 2 : (BN == 256 ? 3 : (BN == 128 ? 4 : 6));   // activation-tile ring, as deep as shared memory allows
+    // The dequantised weight tiles have a ring of their own.  With 512-token tiles it is one deeper than the
+    // activation ring: with two slots only ONE stage can be dequantised at a time (the other slot belongs to
+    // the running MMAs), and a stage's dequantisation - latency-bound bursts on all sixteen warps - takes
+    // twice as long as its MMAs; with three, two stages are in dequantisation while the third is multiplied.
+    static constexpr int ASTAGES = BN > 256 ? 3 : STAGES;
     static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // dequantised weight tile + activation tiles
-    // The index boxes have a ring of their own, deeper than the stages: they come from HBM and are
-    // consumed by the dequantising warps long before the stage's MMAs retire.  (With the box inside the
-    // stage, a two-stage kernel had the HBM round trip of the indices in series with dequantisation
-    // and the MMAs of every stage.)
-    static constexpr int NIDX = BN > 256 ? 4 : (BN == 256 ? 6 : (BN == 128 ? 8 : 6));
-    static constexpr int IDX_OFFSET = LUT_BYTES + STAGES * STAGE_BYTES;
+    // The index boxes have a ring too: they come from HBM and are consumed by the dequantising warps
+    // long before the stage's MMAs retire.  (With the box inside the stage, a two-stage kernel had the HBM
+    // round trip of the indices in series with dequantisation and the MMAs of every stage.)
+    static constexpr int NIDX = BN > 256 ? 2 : (BN == 256 ? 6 : (BN == 128 ? 8 : 6));
+    static constexpr int A_OFFSET = LUT_BYTES;
+    static constexpr int B_OFFSET = A_OFFSET + ASTAGES * A_BYTES;
+    static constexpr int IDX_OFFSET = B_OFFSET + STAGES * B_BYTES;
     static constexpr int BAR_OFFSET = IDX_OFFSET + NIDX * IDX_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;  // barriers + slack for 1024-byte alignment
     static_assert(TOTAL <= 232448, "stages + index ring must fit one SM's shared memory");
@@ -100,22 +105,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_x,
             const GemmArgs a) {
     using S = Smem<BN>;
-    constexpr int STAGES = S::STAGES;
+    constexpr int STAGES = S::STAGES;      // activation tiles
+    constexpr int ASTAGES = S::ASTAGES;    // dequantised weight tiles
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     char* lut = smem;
-    char* stage0 = smem + LUT_BYTES;
+    char* a0 = smem + S::A_OFFSET;
+    char* b0 = smem + S::B_OFFSET;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
     constexpr int NIDX = S::NIDX;
     char* idx0 = smem + S::IDX_OFFSET;
     uint64_t* b_full = bars;                    // [STAGES] activation tiles landed
-    uint64_t* a_full = bars + STAGES;           // [STAGES] bf16 weight tile written
-    uint64_t* empty = bars + 2 * STAGES;        // [STAGES] UMMAs of the stage retired: its A and B tiles are free
-    uint64_t* idx_full = bars + 3 * STAGES;     // [NIDX] index box landed
+    uint64_t* empty = bars + STAGES;            // [STAGES] UMMAs of the stage retired: its activation tiles are free
+    uint64_t* a_full = bars + 2 * STAGES;       // [ASTAGES] bf16 weight tile written
+    uint64_t* a_free = a_full + ASTAGES;        // [ASTAGES] UMMAs that read the weight tile retired
+    uint64_t* idx_full = a_free + ASTAGES;      // [NIDX] index box landed
     uint64_t* idx_free = idx_full + NIDX;       // [NIDX] index box read by every dequantising warp
     uint64_t* acc_full = idx_free + NIDX;       // accumulator complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
-    static_assert((3 * 6 + 2 * 8 + 2) * 8 <= 512, "barrier area");
+    static_assert((4 * 6 + 2 * 8 + 2) * 8 <= 512, "barrier area");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -129,8 +137,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             sm100::mbar_init(&b_full[s], 1);
-            sm100::mbar_init(&a_full[s], NUM_DEQ_WARPS);
             sm100::mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < ASTAGES; ++s) {
+            sm100::mbar_init(&a_full[s], NUM_DEQ_WARPS);
+            sm100::mbar_init(&a_free[s], 1);
         }
         for (int s = 0; s < NIDX; ++s) {
             sm100::mbar_init(&idx_full[s], 1);
@@ -157,35 +168,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int armed = 0, armed_idx = 0;
-            auto load_idx = [&](int ki) {      // index box of stage ki into ring slot ki % NIDX
-                const int si = ki % NIDX;
-                sm100::mbar_arrive_expect_tx(&idx_full[si], (uint32_t)IDX_BYTES);
-                sm100::tma_load_2d(idx0 + si * IDX_BYTES, &map_idx, &idx_full[si], (KS0 + ki) * BK, o0);
-                armed_idx = ki + 1;
-            };
-            for (int ki = 0; ki < NIDX - 1 && ki < KS; ++ki) load_idx(ki);
+            int armed = 0;
             for (int ks = 0; ks < KS; ++ks) {
                 const int s = ks % STAGES;
                 const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
                 if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-                char* st = stage0 + s * S::STAGE_BYTES;
+                char* bt = b0 + s * S::B_BYTES;
                 sm100::mbar_arrive_expect_tx(&b_full[s], (uint32_t)S::B_BYTES);
 #pragma unroll
                 for (int n = 0; n < S::NSUB; ++n)
-                    sm100::tma_load_2d(st + A_BYTES + n * (S::BNS * BK * 2), &map_x, &b_full[s], (KS0 + ks) * BK, m0 + n * S::BNS);
+                    sm100::tma_load_2d(bt + n * (S::BNS * BK * 2), &map_x, &b_full[s], (KS0 + ks) * BK, m0 + n * S::BNS);
                 armed = ks + 1;
-                // then the index box NIDX - 1 stages ahead: its slot held stage ks - 1
-                const int ki = ks + NIDX - 1;
-                if (ki < KS) {
-                    if (ks >= 1 && !sm100::mbar_wait(&idx_free[ki % NIDX], (uint32_t)(ki / NIDX - 1) & 1u, abort_flag)) break;
-                    load_idx(ki);
-                }
             }
             if (*abort_flag != 0) {
                 // gave up: let copies already in flight land before the CTA retires
                 for (int ks = (armed > STAGES ? armed - STAGES : 0); ks < armed; ++ks)
                     sm100::mbar_wait(&b_full[ks % STAGES], (uint32_t)(ks / STAGES) & 1u, abort_flag, 200000000LL);
+            }
+        }
+    } else if (warp == 2 + NUM_DEQ_WARPS) {
+        // ------------------------------------------------------------ index producer (TMA), a warp of its own:
+        // its only condition is "the box was read", which must not queue behind the activation ring's
+        if (lane == 0) {
+            int armed_idx = 0;
+            for (int ki = 0; ki < KS; ++ki) {
+                const int si = ki % NIDX;
+                if (ki >= NIDX && !sm100::mbar_wait(&idx_free[si], (uint32_t)(ki / NIDX - 1) & 1u, abort_flag)) break;
+                sm100::mbar_arrive_expect_tx(&idx_full[si], (uint32_t)IDX_BYTES);
+                sm100::tma_load_2d(idx0 + si * IDX_BYTES, &map_idx, &idx_full[si], (KS0 + ki) * BK, o0);
+                armed_idx = ki + 1;
+            }
+            if (*abort_flag != 0) {
                 for (int ki = (armed_idx > NIDX ? armed_idx - NIDX : 0); ki < armed_idx; ++ki)
                     sm100::mbar_wait(&idx_full[ki % NIDX], (uint32_t)(ki / NIDX) & 1u, abort_flag, 200000000LL);
             }
@@ -196,22 +209,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
             constexpr uint32_t idesc = sm100::make_idesc_bf16(BM, S::BNS);
             bool ok = true;
             for (int ks = 0; ks < KS && ok; ++ks) {
-                const int s = ks % STAGES;
-                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
-                ok = sm100::mbar_wait(&b_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[s], ph, abort_flag);
+                const int s = ks % STAGES, sa = ks % ASTAGES;
+                const uint32_t ph = (uint32_t)(ks / STAGES) & 1u, pha = (uint32_t)(ks / ASTAGES) & 1u;
+                ok = sm100::mbar_wait(&b_full[s], ph, abort_flag) && sm100::mbar_wait(&a_full[sa], pha, abort_flag);
                 if (!ok) break;
                 sm100::tc_fence_after_sync();
-                char* st = stage0 + s * S::STAGE_BYTES;
-                const uint64_t da = sm100::make_desc_k_sw128(sm100::smem_u32(st));
+                char* bt = b0 + s * S::B_BYTES;
+                const uint64_t da = sm100::make_desc_k_sw128(sm100::smem_u32(a0 + sa * A_BYTES));
 #pragma unroll
                 for (int n = 0; n < S::NSUB; ++n) {    // accumulator n: TMEM columns [n * BNS, +BNS)
-                    const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(st + A_BYTES + n * (S::BNS * BK * 2)));
+                    const uint64_t db = sm100::make_desc_k_sw128(sm100::smem_u32(bt + n * (S::BNS * BK * 2)));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)   // +32 bytes (>> 4 = 2) per 16-element K slice
                         sm100::umma_bf16(tmem_base + (uint32_t)(n * S::BNS), da + 2 * kk, db + 2 * kk, idesc,
                                          (ks > 0 || kk > 0) ? 1u : 0u);
                 }
-                sm100::umma_commit(&empty[s]);
+                sm100::umma_commit(&empty[s]);      // the activation tiles of the stage ...
+                sm100::umma_commit(&a_free[sa]);    // ... and its weight tile are free when these MMAs have retired
             }
             if (ok) sm100::umma_commit(acc_full);
         }
@@ -263,8 +277,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
         }
 
         for (int ks = 0; ks < KS; ++ks) {
-            const int s = ks % STAGES;
-            const uint32_t ph = (uint32_t)(ks / STAGES) & 1u;
+            const int sa = ks % ASTAGES;
+            const uint32_t pha = (uint32_t)(ks / ASTAGES) & 1u;
 #pragma unroll
             for (int p = 0; p < PASSES; ++p) { sc_c[p] = sc_n[p]; of_c[p] = of_n[p]; }
             if (ks + 1 < KS) {  // next step's scale/offset go out before we block
@@ -272,11 +286,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
                 for (int p = 0; p < PASSES; ++p) load_st(ks + 1, o0 + r_a + 8 * p, sc_n[p], of_n[p]);
             }
             const int si = ks % NIDX;
-            // the stage's index box has landed, and the A tile of this stage slot is free (the MMAs that read it
-            // STAGES steps ago have retired; parity 1 on a fresh barrier passes at once)
+            // the stage's index box has landed, and the weight-tile slot is free (the MMAs that read it
+            // ASTAGES steps ago have retired; parity 1 on a fresh barrier passes at once)
             if (!sm100::mbar_wait(&idx_full[si], (uint32_t)(ks / NIDX) & 1u, abort_flag)) break;
-            if (!sm100::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-            char* st = stage0 + s * S::STAGE_BYTES;
+            if (!sm100::mbar_wait(&a_free[sa], pha ^ 1u, abort_flag)) break;
+            char* st = a0 + sa * A_BYTES;
             const char* idx_s = idx0 + si * IDX_BYTES;
 
 #pragma unroll
@@ -330,7 +344,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__
             __syncwarp();
             if (lane == 0) {
                 sm100::mbar_arrive(&idx_free[si]);     // the box has been read (sidecar patch included)
-                sm100::mbar_arrive(&a_full[s]);
+                sm100::mbar_arrive(&a_full[sa]);
             }
         }
 
