@@ -6,20 +6,22 @@
 // Only here is the path a dense contraction, so only here tensor cores are used.
 // One CTA owns a 128 x BN output tile; per 64-column K step
 //
-//   warp 0   (1 lane)  TMA: 128x64 index bytes and BN x 64 bf16 activations (128-byte
-//                      swizzle) -> shared memory, completion on an mbarrier
-//   warps 2-17         dequantise the index tile to bf16 in the UMMA K-major
-//                      128B-swizzled layout: lane-replicated codebook lookup, group
-//                      affine in fp32, sidecar deltas folded in (each row's CSR cursor
-//                      walks forward as K advances), proxy fence, arrive
-//   warp 1   (1 lane)  4 x tcgen05.mma (K = 16 each) accumulating fp32 in TMEM;
-//                      tcgen05.commit frees the stage
+//   warp 0   (1 lane)  TMA: BN x 64 bf16 activations (128-byte swizzle) -> the activation ring
+//   warp 18  (1 lane)  TMA: 128 x 64 index bytes -> the index ring (a warp of its own: its only
+//                      condition, "the box was read", must not queue behind the activation ring's)
+//   warps 2-17         dequantise the index box to bf16 in the UMMA K-major 128B-swizzled layout
+//                      into the weight-tile ring: lane-replicated codebook lookup, group affine
+//                      in fp32, sidecar deltas folded in (each row's CSR cursor walks forward as
+//                      K advances), proxy fence, arrive
+//   warp 1   (1 lane)  4 x tcgen05.mma (K = 16 each) per accumulator, fp32 in TMEM; two
+//                      tcgen05.commit free the stage's activation tiles and its weight tile
 //
 // and after the last step the dequantising warps read TMEM (tcgen05.ld), add the bias and store
-// y[m, o].  Two to six stages (as many as fit for the tile width); every mbarrier wait is bounded and raises a status word.
-// The eight dequantising warps pace the kernel (about 800 issue cycles per K step against 525
-// tensor cycles for a 128x256x64 step), so the token tile is made as wide as TMEM allows: at
-// BN = 512 every dequantised tile feeds twice the tensor work.
+// y[m, o].  Three rings (activation tiles, weight tiles, index boxes: see Smem); every mbarrier wait
+// is bounded and raises a status word.  The dequantising warps pace the kernel (a warp's chain per
+// step - two waits, index load, 16 dependent lookups, stores, fence, arrival - takes about twice
+// as long as the step's MMAs), so the token tile is made as wide as TMEM allows: at BN = 512 every
+// dequantised tile feeds twice the tensor work.
 // No cluster launch and no multicast anywhere.
 
 #include <cuda.h>
