@@ -671,7 +671,8 @@ int run(const hxq_desc* d, const __nv_bfloat16* xb, int64_t ldxb, int32_t M, voi
         const int per_block = 4 / H;      // stages per block of four boxes (scale/offset staging works in such blocks)
         a.k_per_split = ((a.k_steps + splits - 1) / splits + per_block - 1) / per_block * per_block;
         splits = (a.k_steps + a.k_per_split - 1) / a.k_per_split;   // no empty slice
-        a.partial = reinterpret_cast<float*>(split_ws);
+        if (splits > 1) a.partial = reinterpret_cast<float*>(split_ws);
+        else a.k_per_split = a.k_steps;                             // one slice after rounding: nothing to split
     } else {
         splits = 1;
     }
