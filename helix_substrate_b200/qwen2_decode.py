@@ -440,7 +440,9 @@ def run_decode(shape: str, batches, prompt: int, new_tokens: int, device, rank: 
                         view.copy_(torch.randn(view.shape, device=device, generator=g) * 0.5)
                 nxt = ids[:, -1].clone()
             else:
-                model.prefill(ids[:, : min(prompt, 64)])            # warm-up call (first-use set-up of every kernel)
+                # warm-up call: first-use set-up of every kernel and every workspace the timed call needs (the whole
+                # prompt when that is cheap, else enough tokens to reach the large-token kernel)
+                model.prefill(ids if batch * prompt <= 4096 else ids[:, : min(prompt, 600)])
                 torch.cuda.synchronize(device)
                 p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 p0.record()
