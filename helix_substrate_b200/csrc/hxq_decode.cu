@@ -586,9 +586,19 @@ static int launch_dense_gemv(const __nv_bfloat16* W, int64_t ldw, int n_out, int
             return HXQ_E_SHAPE;
         smem_set[dev] = smem;
     }
-    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, dense_gemv_kernel<MP>, 256, smem) != cudaSuccess || occ < 1) occ = 1;
-    int grid = n_sm * occ;
+    // SM count and resident CTAs per SM, asked once per device and shared-memory size
+    static int sm_cached[64] = {0}, occ_cached[64] = {0};
+    static size_t occ_smem[64] = {0};
+    if (sm_cached[dev] == 0) {
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+        sm_cached[dev] = n_sm;
+    }
+    if (occ_cached[dev] == 0 || occ_smem[dev] != smem) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, dense_gemv_kernel<MP>, 256, smem) != cudaSuccess || occ < 1) occ = 1;
+        occ_cached[dev] = occ;
+        occ_smem[dev] = smem;
+    }
+    int grid = sm_cached[dev] * occ_cached[dev];
     const int need = (n_out + 31) / 32;      // eight warps of four rows per CTA
     if (grid > need) grid = need;
     const cudaError_t e = launch_pdl(dense_gemv_kernel<MP>, dim3(grid), dim3(256), smem, stream, W, ldw, n_out, n_in, x, ldx, y,
